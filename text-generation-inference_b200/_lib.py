@@ -124,11 +124,60 @@ SIGNATURES.update({
     "b200_llama_step": (_I, [_WP, _SP, _P]),
 })
 
+# libb200_seq.so (include/b200_seq.h): the kernels of the hybrid decoder families.  It also carries the block allocator and the
+# error / launch-count entry points, so a process that serves such a model needs no other library.
+SEQ_LIB_PATH = os.path.join(_HERE, "libb200_seq.so")
+SEQ_SIGNATURES = {
+    "b200_seq_linear": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _P, _I, _L, _L, _L, _L, _L, _L, _P]),
+    "b200_seq_embed_scale": (_I, [_P, _I, _P, _F, _P, _L, _L, _L, _P]),
+    "b200_seq_layernorm": (_I, [_P, _I, _P, _P, _I, _P, _P, _L, _L, _F, _P]),
+    "b200_seq_group_rmsnorm_gate": (_I, [_P, _L, _P, _L, _I, _P, _I, _I, _I, _F, _P, _I, _L, _L, _P]),
+    "b200_seq_ff_clamped_gate": (_I, [_P, _P, _I, _L, _L, _F, _F, _P]),
+    "b200_seq_token_side": (_I, [_P, _P, _P, _L, _L, _I, _L, _P, _P, _P, _I, _L, _L, _F, _P]),
+    "b200_seq_latent_prepare": (_I, [_P, _L, _I, _I, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _F, _P]),
+    "b200_seq_latent_attn": (_I, [_P, _P, _I, _P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _P]),
+    "b200_seq_causal_conv_silu": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _I, _P]),
+    "b200_seq_ssm_scan": (_I, [_P, _L, _I, _I, _I, _P, _L, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
+    "b200_seq_mlstm_scan": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _F, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),
+}
+_SEQ_SHARED = ("b200_last_error", "b200_cuda_peek_error", "b200_launch_count", "b200_kv_alloc_create", "b200_kv_alloc_destroy",
+               "b200_kv_alloc_num_free", "b200_kv_alloc_take", "b200_kv_alloc_release", "b200_decode_advance")
+
 _lib = None
+_seq_lib = None
 
 
 class B200Error(RuntimeError):
     pass
+
+
+def load_seq() -> ctypes.CDLL:
+    """Loads libb200_seq.so, compiling it in the tree first when it is absent or older than its sources (nvcc needs no GPU)."""
+    global _seq_lib
+    if _seq_lib is None:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_b200_build", os.path.join(_HERE, "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        try:
+            mod.build(target="seq")
+        except Exception as e:
+            if not os.path.exists(SEQ_LIB_PATH):
+                raise B200Error(f"{SEQ_LIB_PATH} could not be built: {e}")
+        lib = ctypes.CDLL(SEQ_LIB_PATH)
+        for name, (res, args) in SEQ_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        for name in _SEQ_SHARED:
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = SIGNATURES[name]
+        _seq_lib = lib
+    return _seq_lib
+
+
+def check_seq(status: int, what: str) -> None:
+    if status != 0:
+        raise B200Error(f"{what} failed with status {status}: {load_seq().b200_last_error().decode()}")
 
 
 def load() -> ctypes.CDLL:

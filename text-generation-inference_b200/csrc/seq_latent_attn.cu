@@ -1,0 +1,202 @@
+// Latent attention over a paged latent cache.
+//
+// A token caches ONE row of D = R + r elements per layer: its normalised latent c (R) and its rotated shared key part (r).
+// Attention runs in the absorbed form: a head's query is carried into latent space once (q~ = Wuk_h^T q_plain, done by the
+// per-head product in seq_linear.cu), so that score(i, j) = (q~_i . c_j + qrot_i . krot_j) * scale and the head's output is
+// Wuv_h (sum_j p_ij c_j): every head reads the same cache row, nothing per head is ever stored.
+//
+//   latent_prepare_kernel : RMS-norms the latent slice of the down-projection, rotates the shared key part, writes both into the
+//                           token's cache slot; rotates each head's query part into the absorbed-query buffer.
+//   latent_attn_kernel    : one block per (query token, group of heads), one warp per head; streams the visible window
+//                           [p - window + 1, p] of the sequence's pages in tiles of 32 keys through shared memory, fp32 online
+//                           soft-max.  Serves prompts, portions of prompts that follow cached tokens and single decoded tokens
+//                           alike: a query's keys are always read back from the cache, whatever step wrote them.
+//
+// Rotation: interleaved pairs (2i, 2i+1) of the first `rot_dims` elements, angle tables [positions, rot_dims/2] (fp32, made
+// by the host with any frequency scaling and amplitude factor folded in); elements past rot_dims pass unchanged.
+#include "seq_common.cuh"
+
+namespace b200 {
+namespace seq {
+
+constexpr int kPrepThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepThreads) latent_prepare_kernel(
+    const float* __restrict__ down, int64_t ld_down, int col_c, int col_kr,  // down-projection row: latent at col_c, key part at col_kr
+    const float* __restrict__ q, int64_t ld_q, int q_head_stride, int q_rot_off,  // per head: rotated part at h*stride + off
+    const T* __restrict__ cnorm_w, const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int64_t* __restrict__ position_ids,
+    const int64_t* __restrict__ slot_mapping, T* __restrict__ cache, float* __restrict__ q_abs, int H, int R, int r, int rot_dims, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const int D = R + r, half = rot_dims / 2;
+  const int64_t pos = position_ids[t];
+  const int64_t slot = slot_mapping[t];
+  const float* crow = down + t * ld_down + col_c;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < R; i += kPrepThreads) s += crow[i] * crow[i];
+  const float rstd = 1.f / sqrtf(block_sum(s, red) / R + eps);
+  const float* cs = cos_t + pos * half;
+  const float* sn = sin_t + pos * half;
+  if (slot >= 0) {
+    T* dst = cache + slot * D;
+    for (int i = threadIdx.x; i < R; i += kPrepThreads) stf(dst + i, crow[i] * rstd * ldf(cnorm_w + i));
+    const float* kr = down + t * ld_down + col_kr;
+    for (int i = threadIdx.x; i < r; i += kPrepThreads) {
+      float v;
+      if (i < rot_dims) {
+        const int p = i >> 1;
+        const float a = kr[2 * p], b = kr[2 * p + 1];
+        v = (i & 1) ? b * cs[p] + a * sn[p] : a * cs[p] - b * sn[p];
+      } else {
+        v = kr[i];
+      }
+      stf(dst + R + i, v);
+    }
+  }
+  for (int idx = threadIdx.x; idx < H * r; idx += kPrepThreads) {
+    const int h = idx / r, i = idx % r;
+    const float* qr = q + t * ld_q + (int64_t)h * q_head_stride + q_rot_off;
+    float v;
+    if (i < rot_dims) {
+      const int p = i >> 1;
+      const float a = qr[2 * p], b = qr[2 * p + 1];
+      v = (i & 1) ? b * cs[p] + a * sn[p] : a * cs[p] - b * sn[p];
+    } else {
+      v = qr[i];
+    }
+    q_abs[(t * H + h) * D + R + i] = v;
+  }
+}
+
+constexpr int kHeadsPerBlock = 8, kKeyTile = 32;
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(kHeadsPerBlock * 32) latent_attn_kernel(
+    const float* __restrict__ q_abs, const T* __restrict__ cache, const int32_t* __restrict__ block_table, int64_t bt_stride,
+    const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H, int R, int D, int window,
+    float scale, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* qs = sm;                        // [kHeadsPerBlock][D]
+  float* ks = sm + kHeadsPerBlock * D;   // [kKeyTile][D + 1]
+  const int64_t t = blockIdx.x;
+  const int h0 = blockIdx.y * kHeadsPerBlock;
+  const int w = warp_id(), lane = lane_id();
+  const int h = h0 + w;
+  const int b = seq_of_token[t];
+  const int p = (int)position_ids[t];
+  const int j_lo = max(0, p - window + 1);
+  const int nthreads = kHeadsPerBlock * 32;
+  for (int idx = threadIdx.x; idx < kHeadsPerBlock * D; idx += nthreads) {
+    const int hh = h0 + idx / D;
+    qs[idx] = hh < H ? q_abs[(t * H + hh) * D + idx % D] : 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  float acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) acc[i] = 0.f;
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  for (int j0 = j_lo; j0 <= p; j0 += kKeyTile) {
+    __syncthreads();  // the previous tile is consumed (and qs is written, first time round)
+    const int nk = min(kKeyTile, p - j0 + 1);
+    for (int idx = threadIdx.x; idx < nk * D; idx += nthreads) {
+      const int jj = idx / D, dd = idx % D;
+      const int j = j0 + jj;
+      const int64_t row = (int64_t)table[j / page] * page + j % page;
+      ks[jj * (D + 1) + dd] = ldf(cache + row * D + dd);
+    }
+    __syncthreads();
+    if (h < H) {
+      float s = -INFINITY;
+      if (lane < nk) {
+        float a = 0.f;
+        const float* kq = ks + lane * (D + 1);
+        const float* qq = qs + w * D;
+        for (int d = 0; d < D; ++d) a = fmaf(qq[d], kq[d], a);
+        s = a * scale;
+      }
+      const float m_new = fmaxf(m, warp_max(s));
+      const float pr = lane < nk ? expf(s - m_new) : 0.f;
+      const float corr = expf(m - m_new);  // m = -inf on the first tile: 0
+      l = l * corr + warp_sum(pr);
+      m = m_new;
+#pragma unroll
+      for (int i = 0; i < NR; ++i) acc[i] *= corr;
+      for (int jj = 0; jj < nk; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pr, jj);
+        const float* kr = ks + jj * (D + 1);
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int d = lane + 32 * i;
+          if (d < R) acc[i] = fmaf(pj, kr[d], acc[i]);
+        }
+      }
+    }
+  }
+  if (h < H) {
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int d = lane + 32 * i;
+      if (d < R) out[(t * H + h) * R + d] = acc[i] * inv;
+    }
+  }
+}
+
+}  // namespace seq
+}  // namespace b200
+
+using namespace b200::seq;
+
+extern "C" int b200_seq_latent_prepare(const float* down, int64_t ld_down, int col_c, int col_kr, const float* q, int64_t ld_q, int q_head_stride,
+                                       int q_rot_off, const void* cnorm_w, const float* cos_t, const float* sin_t, const int64_t* position_ids,
+                                       const int64_t* slot_mapping, void* cache, int dt, float* q_abs, int64_t T, int H, int R, int r, int rot_dims,
+                                       float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  if (rot_dims % 2 != 0 || rot_dims > r || rot_dims < 0) { b200_set_last_error("seq_latent_prepare: rot_dims must be even and <= r"); return B200_ERR_ARG; }
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((latent_prepare_kernel<E>), dim3((unsigned)T), dim3(kPrepThreads), 0, (cudaStream_t)stream, down, ld_down, col_c,
+                                       col_kr, q, ld_q, q_head_stride, q_rot_off, (const E*)cnorm_w, cos_t, sin_t, position_ids, slot_mapping,
+                                       (E*)cache, q_abs, H, R, r, rot_dims, eps));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+template <typename T, int NR>
+static int launch_latent_attn(const float* q_abs, const void* cache, const int32_t* block_table, int64_t bt_stride, const int32_t* seq_of_token,
+                              const int64_t* position_ids, float* out, int64_t Tq, int H, int R, int D, int window, float scale, int page,
+                              cudaStream_t st) {
+  const size_t smem = ((size_t)kHeadsPerBlock * D + (size_t)kKeyTile * (D + 1)) * 4;
+  if (smem > 200 * 1024) { b200_set_last_error("seq_latent_attn: cache row too wide"); return B200_ERR_ARG; }
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(latent_attn_kernel<T, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; }
+  dim3 grid((unsigned)Tq, (unsigned)((H + kHeadsPerBlock - 1) / kHeadsPerBlock));
+  B200_LAUNCH((latent_attn_kernel<T, NR>), grid, dim3(kHeadsPerBlock * 32), smem, st, q_abs, (const T*)cache, block_table, bt_stride, seq_of_token,
+              position_ids, out, H, R, D, window, scale, page);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// q_abs [Tq, H, D] fp32; cache [blocks, page, D] of type dt; out [Tq, H, R] fp32.  window <= 0: every earlier token is visible.
+extern "C" int b200_seq_latent_attn(const float* q_abs, const void* cache, int dt, const int32_t* block_table, int64_t bt_stride,
+                                    const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int R, int r,
+                                    int window, float scale, int page, void* stream) {
+  if (Tq == 0) return B200_OK;
+  const int D = R + r;
+  if (window <= 0) window = 0x3fffffff;
+  const int nr = (R + 31) / 32;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LA(NR)                                                                                                                         \
+  B200_SEQ_DISPATCH(dt, E, return (launch_latent_attn<E, NR>(q_abs, cache, block_table, bt_stride, seq_of_token, position_ids, out, Tq, H, R, D, \
+                                                            window, scale, page, st)))
+  if (nr <= 4) LA(4);
+  else if (nr <= 8) LA(8);
+  else if (nr <= 16) LA(16);
+  else if (nr <= 32) LA(32);
+#undef LA
+  b200_set_last_error("seq_latent_attn: latent wider than 1024");
+  return B200_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,217 @@
+// Row kernels around an fp32 residual stream: scaled embedding lookup, layer norm in and out of the stream, RMS norm of a
+// column slice, grouped RMS norm with a gate, the clamped gated feed-forward activation, and the per-layer token side input.
+// One block per token row; all statistics and the residual sum in fp32.
+#include "seq_common.cuh"
+
+namespace b200 {
+namespace seq {
+
+constexpr int kRowThreads = 256;
+
+// x[t, :] = table[id[t], :] * scale  (fp32 residual stream)
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) embed_scale_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, float scale,
+                                                                  float* __restrict__ out, int W, int64_t V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  int64_t id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) out[t * W + i] = ldf(table + id * W + i) * scale;
+}
+
+// mode 0: out[t] = LN(x[t]) * w + b  (x fp32 or T, out T)      mode 1: resid[t] += LN(x[t]) * w + b  (resid fp32)
+template <typename TX, typename TP, typename TO>
+__global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const TX* __restrict__ x, const TP* __restrict__ w, const TP* __restrict__ b,
+                                                                TO* __restrict__ out, float* __restrict__ resid, int W, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float v = ldf(x + t * W + i);
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float y = (row[i] - mean) * rstd * ldf(w + i) + ldf(b + i);
+    if (resid) resid[t * W + i] += y;
+    else stf(out + t * W + i, y);
+  }
+}
+
+// out[t, g*n + i] = gate_after * w[g*n+i] * v / sqrt(mean_i(v^2) + eps), v = x[t, g*n + i] * gate_before, per group g of n
+// columns.  gate kinds: 0 none, 1 SiLU(gate) multiplied in before the statistics, 2 sigmoid(gate) multiplied in after the
+// weight.  groups == 0: no normalisation (gate only).  x and gate are column slices (leading dimensions given) of fp32 buffers.
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kRowThreads) group_rmsnorm_gate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ gate,
+                                                                         int64_t ldg, int gate_kind, const TP* __restrict__ w, int groups, int n,
+                                                                         float eps, TO* __restrict__ out, int64_t ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  const int ng = groups > 0 ? groups : 1;
+  for (int g = 0; g < ng; ++g) {
+    float q = 0.f;
+    if (groups > 0) {
+      for (int i = threadIdx.x; i < n; i += kRowThreads) {
+        float v = x[t * ldx + g * n + i];
+        if (gate_kind == 1) v *= silu_f(gate[t * ldg + g * n + i]);
+        q += v * v;
+      }
+      q = block_sum(q, red);
+    }
+    const float rstd = groups > 0 ? 1.f / sqrtf(q / n + eps) : 1.f;
+    for (int i = threadIdx.x; i < n; i += kRowThreads) {
+      const int c = g * n + i;
+      float v = x[t * ldx + c];
+      if (gate_kind == 1) v *= silu_f(gate[t * ldg + c]);
+      v *= rstd;
+      if (w) v *= ldf(w + c);
+      if (gate_kind == 2) v *= sigmoid_f(gate[t * ldg + c]);
+      stf(out + t * ldo + c, v);
+    }
+  }
+}
+
+// y = g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu = [g | u] per row
+template <typename T>
+__global__ void ff_clamped_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int F, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * F;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / F, c = i % F;
+    const float g = fminf(ldf(gu + r * 2 * F + c), limit);
+    const float u = fminf(fmaxf(ldf(gu + r * 2 * F + F + c), -limit), limit);
+    stf(out + i, g * sigmoid_f(alpha * g) * (u + 1.f));
+  }
+}
+
+// Per-layer token input added to the stream: e = side_table[id, col0 : col0 + dim]; g = gelu_tanh(Wg x) * e; y = Wp g;
+// x += y / sqrt(mean(y^2) + eps) * nw.   Wg [dim, W], Wp [W, dim].  dim is small (tens): one block does the row.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) token_side_kernel(float* __restrict__ resid, const int64_t* __restrict__ ids, const T* __restrict__ table,
+                                                                 int64_t ld_table, int64_t col0, int dim, int64_t V, const T* __restrict__ Wg,
+                                                                 const T* __restrict__ Wp, const T* __restrict__ nw, int W, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* xs = sm;       // [W]
+  float* gs = sm + W;   // [dim]
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  int64_t id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) xs[i] = resid[t * W + i];
+  __syncthreads();
+  for (int j = warp_id(); j < dim; j += kRowThreads / 32) {
+    float a = 0.f;
+    for (int i = lane_id(); i < W; i += 32) a = fmaf(ldf(Wg + (int64_t)j * W + i), xs[i], a);
+    a = warp_sum(a);
+    if (lane_id() == 0) gs[j] = gelu_tanh_f(a) * ldf(table + id * ld_table + col0 + j);
+  }
+  __syncthreads();
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    float y = 0.f;
+    for (int j = 0; j < dim; ++j) y = fmaf(ldf(Wp + (int64_t)i * dim + j), gs[j], y);
+    q += y * y;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    float y = 0.f;
+    for (int j = 0; j < dim; ++j) y = fmaf(ldf(Wp + (int64_t)i * dim + j), gs[j], y);
+    resid[t * W + i] = xs[i] + y * rstd * ldf(nw + i);
+  }
+}
+
+}  // namespace seq
+}  // namespace b200
+
+using namespace b200::seq;
+
+extern "C" int b200_seq_embed_scale(const void* table, int dt, const int64_t* ids, float scale, float* out, int64_t T, int64_t W, int64_t V,
+                                    void* stream) {
+  if (T == 0) return B200_OK;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((embed_scale_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, (const E*)table, ids,
+                                       scale, out, (int)W, V));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// x_dt: element type of x (fp32 stream or an activation of type dt).  resid == nullptr: out (type dt) = LN(x); else resid += LN(x).
+extern "C" int b200_seq_layernorm(const void* x, int x_dt, const void* w, const void* b, int dt, void* out, float* resid, int64_t T, int64_t W,
+                                  float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  if (W * 4 > 160 * 1024) { b200_set_last_error("seq_layernorm: row too wide"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)W * 4;
+#define LN_LAUNCH(TX, TP)                                                                                                              \
+  do {                                                                                                                                 \
+    static bool cfg = false;                                                                                                           \
+    if (!cfg) { cudaFuncSetAttribute(layernorm_kernel<TX, TP, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; } \
+    B200_LAUNCH((layernorm_kernel<TX, TP, TP>), dim3((unsigned)T), dim3(kRowThreads), smem, st, (const TX*)x, (const TP*)w, (const TP*)b,   \
+                (TP*)out, resid, (int)W, eps);                                                                                         \
+  } while (0)
+  if (dt == B200_DT_F32 && x_dt == B200_DT_F32) LN_LAUNCH(float, float);
+  else if (dt == B200_DT_BF16 && x_dt == B200_DT_F32) LN_LAUNCH(float, __nv_bfloat16);
+  else if (dt == B200_DT_BF16 && x_dt == B200_DT_BF16) LN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else { b200_set_last_error("seq_layernorm: unsupported element types"); return B200_ERR_UNSUPPORTED; }
+#undef LN_LAUNCH
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_group_rmsnorm_gate(const float* x, int64_t ldx, const float* gate, int64_t ldg, int gate_kind, const void* w, int w_dt,
+                                           int groups, int n, float eps, void* out, int out_dt, int64_t ldo, int64_t T, void* stream) {
+  if (T == 0) return B200_OK;
+  if (gate_kind != 0 && gate == nullptr) { b200_set_last_error("seq_group_rmsnorm_gate: gate missing"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+#define GN_LAUNCH(TP, TO)                                                                                                                   \
+  B200_LAUNCH((group_rmsnorm_gate_kernel<TP, TO>), dim3((unsigned)T), dim3(kRowThreads), 0, st, x, ldx, gate, ldg, gate_kind, (const TP*)w, \
+              groups, n, eps, (TO*)out, ldo)
+  if (w_dt == B200_DT_F32 && out_dt == B200_DT_F32) GN_LAUNCH(float, float);
+  else if (w_dt == B200_DT_BF16 && out_dt == B200_DT_BF16) GN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dt == B200_DT_BF16 && out_dt == B200_DT_F32) GN_LAUNCH(__nv_bfloat16, float);
+  else { b200_set_last_error("seq_group_rmsnorm_gate: unsupported element types"); return B200_ERR_UNSUPPORTED; }
+#undef GN_LAUNCH
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_ff_clamped_gate(const void* gu, void* out, int dt, int64_t rows, int64_t F, float limit, float alpha, void* stream) {
+  if (rows == 0 || F == 0) return B200_OK;
+  int64_t blocks = (rows * F + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((ff_clamped_gate_kernel<E>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const E*)gu, (E*)out,
+                                       rows, (int)F, limit, alpha));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_token_side(float* resid, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V,
+                                   const void* Wg, const void* Wp, const void* nw, int dt, int64_t T, int64_t W, float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  const size_t smem = (size_t)(W + dim) * 4;
+  if (smem > 160 * 1024) { b200_set_last_error("seq_token_side: row too wide"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+  B200_SEQ_DISPATCH(dt, E, {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(token_side_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
+    B200_LAUNCH((token_side_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), smem, st, resid, ids, (const E*)table, ld_table, col0, dim, V,
+                (const E*)Wg, (const E*)Wp, (const E*)nw, (int)W, eps);
+  });
+  b200_count_launches(1);
+  return B200_OK;
+}

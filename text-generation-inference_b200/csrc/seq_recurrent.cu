@@ -1,0 +1,338 @@
+// Recurrent mixers with a matrix state per head, carried from token to token in fp32 state slots:
+//
+//   ssm_scan_kernel   (selective state space, "Mamba-2" form)  S_t = a_t S_(t-1) + dt_t B_t x_t^T ,  y_t = S_t^T C_t + D x_t
+//                     a_t = exp(-exp(A_log) dt_t), dt_t = softplus(raw + bias); B / C shared by the heads of a group.
+//   mlstm_scan_kernel (matrix memory with exponential gating)  m_t = max(f_t + m_(t-1), i_t),
+//                     S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T, n_t likewise with k_t alone,
+//                     y_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6); i_t = cap tanh(raw/cap), f_t = logsigmoid(cap tanh(raw/cap)).
+//   causal_conv_silu_kernel / conv_state_update_kernel: short depth-wise causal convolution whose last taps-1 inputs are state.
+//
+// One block owns (sequence, head, 32 value columns) and walks the sequence's tokens of this step in order, whether they are a
+// whole prompt, a portion of one or a single decoded token: the arithmetic per token is the same in every case, so the state
+// and the outputs do not depend on how a sequence was cut into steps.  A thread holds a column's state entries for every 8th
+// state row in registers; 8 neighbouring lanes reduce the read-out.  A sequence whose first token of the step is at position 0
+// starts from a zero state and never reads its (possibly reused) slot.
+#include "seq_common.cuh"
+
+namespace b200 {
+namespace seq {
+
+constexpr int kScanThreads = 256, kCols = 32, kSplit = 8, kChunk = 16;
+
+__device__ __forceinline__ float group8_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+template <typename TP, int KMAX>
+__global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
+    const float* __restrict__ xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* __restrict__ dt_raw, int64_t ld_dt, int col_dt,
+    const TP* __restrict__ dt_bias, const TP* __restrict__ A_log, const TP* __restrict__ Dskip, float* __restrict__ state,
+    const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ y,
+    int64_t ld_y, int H, int P, int N, int heads_per_group) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* Bs = sm;                      // [kChunk][N]
+  float* Cs = Bs + kChunk * N;         // [kChunk][N]
+  float* xs = Cs + kChunk * N;         // [kChunk][kCols]
+  float* ys = xs + kChunk * kCols;     // [kChunk][kCols]
+  float* dts = ys + kChunk * kCols;    // [kChunk]
+  float* dec = dts + kChunk;           // [kChunk]
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
+  const int g = h / heads_per_group;
+  const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
+  const int v = v0 + col;
+  const bool vok = v < P;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (t_begin >= t_end) return;
+  const bool fresh = position_ids[t_begin] == 0;
+  float* sp = state + ((int64_t)state_slots[b] * H + h) * N * P;
+  float S[KMAX];
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    S[i] = (!fresh && vok && n < N) ? sp[(int64_t)n * P + v] : 0.f;
+  }
+  const float bias = ldf(dt_bias + h), A = expf(ldf(A_log + h)), Dh = ldf(Dskip + h);
+  for (int t0 = t_begin; t0 < t_end; t0 += kChunk) {
+    const int nt = min(kChunk, t_end - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * N; idx += kScanThreads) {
+      const int tt = idx / N, n = idx % N;
+      const float* row = xbc + (int64_t)(t0 + tt) * ld_xbc;
+      Bs[tt * N + n] = row[col_B + g * N + n];
+      Cs[tt * N + n] = row[col_C + g * N + n];
+    }
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, c = idx % kCols;
+      xs[idx] = (v0 + c < P) ? xbc[(int64_t)(t0 + tt) * ld_xbc + col_x + h * P + v0 + c] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const float d = softplus_f(dt_raw[(int64_t)(t0 + threadIdx.x) * ld_dt + col_dt + h] + bias);
+      dts[threadIdx.x] = d;
+      dec[threadIdx.x] = expf(-A * d);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float a = dec[tt], xv = xs[tt * kCols + col];
+      const float coef = dts[tt] * xv;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < N) {
+          S[i] = fmaf(a, S[i], coef * Bs[tt * N + n]);
+          part = fmaf(S[i], Cs[tt * N + n], part);
+        }
+      }
+      part = group8_sum(part);
+      if (ks == 0) ys[tt * kCols + col] = part + Dh * xv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, c = idx % kCols;
+      if (v0 + c < P) y[(int64_t)(t0 + tt) * ld_y + h * P + v0 + c] = ys[idx];
+    }
+  }
+  if (vok) {
+#pragma unroll
+    for (int i = 0; i < KMAX; ++i) {
+      const int n = ks + kSplit * i;
+      if (n < N) sp[(int64_t)n * P + v] = S[i];
+    }
+  }
+}
+
+template <typename TP, int KMAX>
+__global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
+    const float* __restrict__ proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const TP* __restrict__ i_bias,
+    const TP* __restrict__ f_bias, float cap, float q_scale, float* __restrict__ S_state, float* __restrict__ n_state, float* __restrict__ m_state,
+    const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ y,
+    int64_t ld_y, int H, int dk, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* qs = sm;                       // [kChunk][dk]
+  float* kk = qs + kChunk * dk;         // [kChunk][dk]
+  float* vs = kk + kChunk * dk;         // [kChunk][kCols]
+  float* ys = vs + kChunk * kCols;      // [kChunk][kCols]
+  float* ig = ys + kChunk * kCols;      // [kChunk]
+  float* fg = ig + kChunk;              // [kChunk]
+  const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
+  const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
+  const int v = v0 + col;
+  const bool vok = v < dv;
+  const int t_begin = cu_q[b], t_end = cu_q[b + 1];
+  if (t_begin >= t_end) return;
+  const bool fresh = position_ids[t_begin] == 0;
+  const int64_t slot = state_slots[b];
+  float* Sp = S_state + (slot * H + h) * dk * dv;
+  float* np = n_state + (slot * H + h) * dk;
+  float S[KMAX], nn[KMAX];
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    S[i] = (!fresh && vok && n < dk) ? Sp[(int64_t)n * dv + v] : 0.f;
+    nn[i] = (!fresh && n < dk) ? np[n] : 0.f;
+  }
+  float m = fresh ? 0.f : m_state[slot * H + h];
+  const float ib = ldf(i_bias + h), fb = ldf(f_bias + h);
+  for (int t0 = t_begin; t0 < t_end; t0 += kChunk) {
+    const int nt = min(kChunk, t_end - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * dk; idx += kScanThreads) {
+      const int tt = idx / dk, n = idx % dk;
+      const float* row = proj + (int64_t)(t0 + tt) * ld;
+      qs[idx] = row[col_q + h * dk + n] * q_scale;
+      kk[idx] = row[col_k + h * dk + n];
+    }
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, c = idx % kCols;
+      vs[idx] = (v0 + c < dv) ? proj[(int64_t)(t0 + tt) * ld + col_v + h * dv + v0 + c] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const float* row = proj + (int64_t)(t0 + threadIdx.x) * ld;
+      ig[threadIdx.x] = cap * tanhf((row[col_i + h] + ib) / cap);
+      fg[threadIdx.x] = logsigmoid_f(cap * tanhf((row[col_f + h] + fb) / cap));
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float fm = fg[tt] + m;
+      const float m_new = fmaxf(fm, ig[tt]);
+      const float keep = expf(fm - m_new), take = expf(ig[tt] - m_new);
+      m = m_new;
+      const float tv = take * vs[tt * kCols + col];
+      float num = 0.f, nq = 0.f;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) {
+          const float kv = kk[tt * dk + n], qv = qs[tt * dk + n];
+          S[i] = fmaf(keep, S[i], kv * tv);
+          nn[i] = fmaf(keep, nn[i], take * kv);
+          num = fmaf(S[i], qv, num);
+          nq = fmaf(nn[i], qv, nq);
+        }
+      }
+      num = group8_sum(num);
+      nq = group8_sum(nq);
+      if (ks == 0) ys[tt * kCols + col] = num / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
+      const int tt = idx / kCols, c = idx % kCols;
+      if (v0 + c < dv) y[(int64_t)(t0 + tt) * ld_y + h * dv + v0 + c] = ys[idx];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    if (n < dk) {
+      if (vok) Sp[(int64_t)n * dv + v] = S[i];
+      if (blockIdx.z == 0 && col == 0) np[n] = nn[i];
+    }
+  }
+  if (blockIdx.z == 0 && threadIdx.x == 0) m_state[slot * H + h] = m;
+}
+
+constexpr int kMaxTaps = 8;
+
+// out[t, c] = silu(bias[c] + sum_j w[c, j] * in(p - (taps-1) + j)), p the token's position; inputs before this step's first token
+// come from the sequence's conv state (positions >= 0) or are zero (before the sequence starts)
+template <typename TP>
+__global__ void causal_conv_silu_kernel(const float* __restrict__ u, int64_t ld_u, int col0, int C, int taps, const TP* __restrict__ w,
+                                        const TP* __restrict__ bias, const float* __restrict__ conv_state, const int32_t* __restrict__ state_slots,
+                                        const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ cu_q,
+                                        const int64_t* __restrict__ position_ids, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int b = seq_of_token[t];
+  const int row0 = cu_q[b];
+  const int64_t s = position_ids[row0], p = position_ids[t];
+  const float* st = conv_state + (int64_t)state_slots[b] * (taps - 1) * C;
+  float acc = ldf(bias + c);
+  for (int j = 0; j < taps; ++j) {
+    const int64_t pp = p - (taps - 1) + j;
+    float val = 0.f;
+    if (pp >= s) val = u[(row0 + (pp - s)) * ld_u + col0 + c];
+    else if (pp >= 0) val = st[(pp - s + taps - 1) * C + c];
+    acc = fmaf(ldf(w + (int64_t)c * taps + j), val, acc);
+  }
+  out[t * C + c] = silu_f(acc);
+}
+
+// after the convolution: the state becomes the last taps-1 inputs of the sequence (older state entries shift when the step
+// brought fewer tokens than that)
+__global__ void conv_state_update_kernel(const float* __restrict__ u, int64_t ld_u, int col0, int C, int taps, float* __restrict__ conv_state,
+                                         const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q,
+                                         const int64_t* __restrict__ position_ids) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int row0 = cu_q[b], nq = cu_q[b + 1] - row0;
+  if (nq <= 0) return;
+  const int64_t s = position_ids[row0], e = s + nq;
+  float* st = conv_state + (int64_t)state_slots[b] * (taps - 1) * C;
+  float old[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) old[k] = (k < taps - 1 && s > 0) ? st[(int64_t)k * C + c] : 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k >= taps - 1) break;
+    const int64_t pp = e - (taps - 1) + k;
+    float val = 0.f;
+    if (pp >= s) val = u[(row0 + (pp - s)) * ld_u + col0 + c];
+    else if (pp >= 0) {
+      const int idx = (int)(pp - s + taps - 1);
+#pragma unroll
+      for (int q = 0; q < kMaxTaps; ++q)
+        if (q == idx) val = old[q];
+    }
+    st[(int64_t)k * C + c] = val;
+  }
+}
+
+}  // namespace seq
+}  // namespace b200
+
+using namespace b200::seq;
+
+extern "C" int b200_seq_causal_conv_silu(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt,
+                                         float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
+                                         const int64_t* position_ids, float* out, int64_t T, int B, void* stream) {
+  if (T == 0) return B200_OK;
+  if (taps < 1 || taps > kMaxTaps) { b200_set_last_error("seq_causal_conv_silu: 1 <= taps <= 8"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned cb = (unsigned)((C + 255) / 256);
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((causal_conv_silu_kernel<E>), dim3((unsigned)T, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, (const E*)w,
+                                       (const E*)bias, (const float*)conv_state, state_slots, seq_of_token, cu_q, position_ids, out));
+  if (taps > 1)
+    B200_LAUNCH(conv_state_update_kernel, dim3((unsigned)B, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, conv_state, state_slots, cu_q, position_ids);
+  b200_count_launches(2);
+  return B200_OK;
+}
+
+template <typename TP, int KMAX>
+static int launch_ssm(const float* xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* dt_raw, int64_t ld_dt, int col_dt,
+                      const void* dt_bias, const void* A_log, const void* Dskip, float* state, const int32_t* state_slots, const int32_t* cu_q,
+                      const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int P, int N, int hpg, cudaStream_t st) {
+  const size_t smem = ((size_t)2 * kChunk * N + 2 * kChunk * kCols + 2 * kChunk) * 4;
+  dim3 grid((unsigned)B, (unsigned)H, (unsigned)((P + kCols - 1) / kCols));
+  B200_LAUNCH((ssm_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, xbc, ld_xbc, col_x, col_B, col_C, dt_raw, ld_dt, col_dt,
+              (const TP*)dt_bias, (const TP*)A_log, (const TP*)Dskip, state, state_slots, cu_q, position_ids, y, ld_y, H, P, N, hpg);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_ssm_scan(const float* xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* dt_raw, int64_t ld_dt, int col_dt,
+                                 const void* dt_bias, const void* A_log, const void* Dskip, int dt, float* state, const int32_t* state_slots,
+                                 const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int P, int N, int groups,
+                                 void* stream) {
+  if (B == 0) return B200_OK;
+  if (groups <= 0 || H % groups != 0 || N > 256) { b200_set_last_error("seq_ssm_scan: need heads % groups == 0 and state <= 256"); return B200_ERR_ARG; }
+  const int hpg = H / groups;
+  cudaStream_t st = (cudaStream_t)stream;
+#define SSM(K)                                                                                                                                  \
+  B200_SEQ_DISPATCH(dt, E, return (launch_ssm<E, K>(xbc, ld_xbc, col_x, col_B, col_C, dt_raw, ld_dt, col_dt, dt_bias, A_log, Dskip, state, state_slots, \
+                                                   cu_q, position_ids, y, ld_y, B, H, P, N, hpg, st)))
+  if (N <= 64) SSM(8);
+  else if (N <= 128) SSM(16);
+  else SSM(32);
+#undef SSM
+}
+
+template <typename TP, int KMAX>
+static int launch_mlstm(const float* proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const void* i_bias, const void* f_bias,
+                        float cap, float q_scale, float* S_state, float* n_state, float* m_state, const int32_t* state_slots, const int32_t* cu_q,
+                        const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, cudaStream_t st) {
+  const size_t smem = ((size_t)2 * kChunk * dk + 2 * kChunk * kCols + 2 * kChunk) * 4;
+  dim3 grid((unsigned)B, (unsigned)H, (unsigned)((dv + kCols - 1) / kCols));
+  B200_LAUNCH((mlstm_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, proj, ld, col_q, col_k, col_v, col_i, col_f, (const TP*)i_bias,
+              (const TP*)f_bias, cap, q_scale, S_state, n_state, m_state, state_slots, cu_q, position_ids, y, ld_y, H, dk, dv);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_mlstm_scan(const float* proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const void* i_bias,
+                                   const void* f_bias, int dt, float cap, float q_scale, float* S_state, float* n_state, float* m_state,
+                                   const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H,
+                                   int dk, int dv, void* stream) {
+  if (B == 0) return B200_OK;
+  if (dk > 256) { b200_set_last_error("seq_mlstm_scan: key size <= 256"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+#define ML(K)                                                                                                                               \
+  B200_SEQ_DISPATCH(dt, E, return (launch_mlstm<E, K>(proj, ld, col_q, col_k, col_v, col_i, col_f, i_bias, f_bias, cap, q_scale, S_state, n_state, \
+                                                     m_state, state_slots, cu_q, position_ids, y, ld_y, B, H, dk, dv, st)))
+  if (dk <= 64) ML(8);
+  else if (dk <= 128) ML(16);
+  else ML(32);
+#undef ML
+}

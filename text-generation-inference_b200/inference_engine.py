@@ -18,7 +18,23 @@ import torch.distributed
 from .utils.dist import initialize_torch_distributed
 from .utils.weights import Weights
 
-FLASH_TYPES = ["llama", "gpt_neox", "gpt_bigcode", "falcon", "RefinedWeb", "RefinedWebModel"]
+FLASH_TYPES = ["llama", "gpt_neox", "gpt_bigcode", "falcon", "RefinedWeb", "RefinedWebModel", "fetotar"]
+# families whose config.json is not a transformers configuration: they name themselves with "architecture"
+OWN_CONFIG_ARCHITECTURES = ("Fetotar",)
+_TOKENIZER_FILES = ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json")
+
+
+def load_config(model_path: str):
+    """the model's configuration object: the family's own reader when config.json names one of OWN_CONFIG_ARCHITECTURES,
+    transformers' AutoConfig otherwise"""
+    import json
+    with open(os.path.join(model_path, "config.json")) as f:
+        raw = json.load(f)
+    if raw.get("architecture") == "Fetotar":
+        from .models.custom_modeling.fetotar_modeling import FetotarConfig
+        return FetotarConfig(raw)
+    from transformers import AutoConfig
+    return AutoConfig.from_pretrained(model_path)
 
 
 def local_weight_files(model_path: str, extension: str = ".safetensors"):
@@ -29,12 +45,12 @@ class InferenceEngine:
     def __init__(self, model_path: str, model_class, dtype: torch.dtype, quantize: Optional[str], model_config: Optional[Any],
                  max_sequence_length: Optional[int], weights: Optional[Weights] = None, tokenizer=None):
         if model_config is None:
-            from transformers import AutoConfig
-            model_config = AutoConfig.from_pretrained(model_path)
+            model_config = load_config(model_path)
         self._config = model_config
-        if tokenizer is None:
+        if tokenizer is None and any(os.path.exists(os.path.join(model_path, f)) for f in _TOKENIZER_FILES):
             from transformers import AutoTokenizer
             tokenizer = AutoTokenizer.from_pretrained(model_path, padding_side="left", truncation_side="left")
+        # no tokenizer files: the model is driven by token ids (FlashCausalLM.step_ragged) or with a tokenizer the caller brings
         self.tokenizer = tokenizer
         self.rank = int(os.getenv("RANK", "0"))
         self.world_size = int(os.getenv("WORLD_SIZE", "1"))
@@ -74,6 +90,13 @@ class InferenceEngine:
                 raise NotImplementedError("alibi is not supported by this version of the model")
             from .models.custom_modeling.flash_rw_modeling import FlashRWForCausalLM
             model_class = FlashRWForCausalLM
+        elif model_type == "fetotar":
+            if quantize is not None:
+                raise ValueError("fetotar checkpoints are served in bfloat16 or float32")
+            if dtype not in (torch.bfloat16, torch.float32):
+                raise ValueError(f"fetotar runs in bfloat16 or float32, not {dtype}")
+            from .models.custom_modeling.fetotar_modeling import FetotarForCausalLM
+            model_class = FetotarForCausalLM
         self._config.quantize = quantize
         self.process_group = initialize_torch_distributed(self.world_size, self.rank)
         self.master = self.rank == 0

@@ -21,9 +21,9 @@ def get_model(model_name: str, revision: Optional[str], deployment_framework: st
     dtype = get_torch_dtype(dtype_str)
     if not os.path.isdir(model_name):
         raise ValueError(f"{model_name!r} is not a local model directory")
-    from transformers import PretrainedConfig
-    config_dict, _ = PretrainedConfig.get_config_dict(model_name)
-    model_type = config_dict["model_type"]
+    from ..inference_engine import load_config
+    config = load_config(model_name)
+    model_type = config.model_type
     if model_type == "gpt2" and "--bigcode--" in model_name:  # tgis_native.py:37-38: starcoder checkpoints
         model_type = "gpt_bigcode"
     if model_type not in FLASH_TYPES:
@@ -33,4 +33,4 @@ def get_model(model_name: str, revision: Optional[str], deployment_framework: st
     if quantize not in (None, "gptq"):
         raise ValueError(f"Unsupported quantization method: {quantize}")
     from .flash_causal_lm import FlashCausalLM
-    return FlashCausalLM(model_name, revision, "tgis_native", dtype, quantize, None, max_sequence_length=max_sequence_length)
+    return FlashCausalLM(model_name, revision, "tgis_native", dtype, quantize, config, max_sequence_length=max_sequence_length)

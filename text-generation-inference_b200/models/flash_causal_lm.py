@@ -27,6 +27,8 @@ from ..utils.tokens import HeterogeneousNextTokenChooser, get_input_tokens_info,
 from .model import Model
 from .types import Batch, GenerateError
 
+import os
+
 USE_CUDA_GRAPHS = __import__("os").getenv("B200_CUDA_GRAPHS", "true").lower() != "false"
 FUSED_CHOOSER = __import__("os").getenv("B200_FUSED_CHOOSER", "1") != "0"
 
@@ -134,7 +136,7 @@ class FlashCausalLMBatch(Batch):
         device = first.cu_seqlens_q.device
         requests, input_lengths, total_lengths, params = [], [], [], []
         cur_tokens, samplings, ret_logprobs = [], [], []
-        input_ids, position_ids, seq_ids, tables, ctx = [], [], [], [], []
+        input_ids, position_ids, seq_ids, tables, ctx, slots = [], [], [], [], [], []
         new_bs = sum(len(b) for b in batches)
         max_total = max(t for b in batches for t in b.total_lengths)
         all_ids = first.all_input_ids_tensor.new_full((new_bs, max_total), first.pad_token_id)
@@ -157,6 +159,7 @@ class FlashCausalLMBatch(Batch):
                 bt = torch.nn.functional.pad(bt, (0, max_cols - bt.shape[1]))
             tables.append(bt)
             ctx.append(kv.context_lens)
+            slots.append(kv.state_slots)
             b.past_key_values = None
             end = start + len(b)
             all_ids[start:end, :b.all_input_ids_tensor.shape[1]] = b.all_input_ids_tensor
@@ -168,7 +171,8 @@ class FlashCausalLMBatch(Batch):
             dtype=fc.dtype, device=fc.device, samplings=samplings, current_tokens=cur_tokens)
         lens_t = torch.tensor([0] + input_lengths, dtype=torch.int32, device=device)
         kv = PagedKVState(sequence_ids=seq_ids, block_table=torch.cat(tables).contiguous(), context_lens=torch.cat(ctx),
-                          slot_mapping=torch.empty(new_bs, dtype=torch.int64, device=device), max_blocks=max_cols)
+                          slot_mapping=torch.empty(new_bs, dtype=torch.int64, device=device), max_blocks=max_cols,
+                          state_slots=torch.cat(slots) if all(x is not None for x in slots) else None)
         return FlashCausalLMBatch(
             batch_id=first.batch_id, requests=requests, input_ids=torch.cat(input_ids), inputs_embeds=None,
             position_ids=torch.cat(position_ids), cu_seqlens=torch.cumsum(lens_t, 0, dtype=torch.int32),
@@ -206,13 +210,16 @@ class FlashCausalLMBatch(Batch):
             kv.block_table = kv.block_table[idx].contiguous()
             kv.context_lens = kv.context_lens[idx].contiguous()
             kv.slot_mapping = kv.slot_mapping[:len(keep)]
+            if kv.state_slots is not None:
+                kv.state_slots = kv.state_slots[idx.to(kv.state_slots.device)].contiguous()
         return batch
 
 
 class FlashCausalLM(Model):
     def __init__(self, model_name: str, revision: Optional[str], deployment_framework: str, dtype: torch.dtype,
                  quantize: Optional[str], model_config: Union[Any] = None, auto_model_class=None,
-                 max_sequence_length: Optional[int] = None, engine=None, num_kv_blocks: Optional[int] = None):
+                 max_sequence_length: Optional[int] = None, engine=None, num_kv_blocks: Optional[int] = None,
+                 num_state_slots: Optional[int] = None):
         if not torch.cuda.is_available():
             raise NotImplementedError("FlashCausalLM is only available on GPU")
         if engine is None:
@@ -221,7 +228,9 @@ class FlashCausalLM(Model):
         super().__init__(engine, dtype, max_sequence_length)
         self.use_position_ids = True
         cfg = self.model.config
-        if getattr(cfg, "pad_token_id", None) is not None:
+        if self.tokenizer is None:
+            pass  # a model folder without tokenizer files: token ids go in and come out (step_ragged, tests with their own tokenizer)
+        elif getattr(cfg, "pad_token_id", None) is not None:
             self.tokenizer.pad_token_id = cfg.pad_token_id
         elif self.tokenizer.pad_token_id is None:
             if getattr(cfg, "eos_token_id", None) is not None:
@@ -230,9 +239,14 @@ class FlashCausalLM(Model):
                 self.tokenizer.pad_token_id = self.tokenizer.eos_token_id
             else:
                 self.tokenizer.add_special_tokens({"pad_token": "[PAD]"})
-        import os
         if num_kv_blocks is None and os.getenv("KV_CACHE_MANAGER_NUM_GPU_BLOCKS"):
             num_kv_blocks = int(os.environ["KV_CACHE_MANAGER_NUM_GPU_BLOCKS"])  # paged_causal_lm.py:310-311
+        if hasattr(self.model, "make_cache_manager"):
+            # families that keep something other than per-head K / V (latent rows, recurrent state) build their own manager
+            slots = int(os.getenv("STATE_CACHE_NUM_SLOTS", "0")) or num_state_slots
+            self.kv_cache_manager = self.model.make_cache_manager(dtype, self.device, num_kv_blocks, slots)
+            self.model.kv_cache_manager = self.kv_cache_manager
+            return
         world = getattr(engine, "world_size", 1)
         kv_heads, kv_world = getattr(cfg, "num_key_value_heads", None) or cfg.num_attention_heads, world
         layout = getattr(type(self.model), "kv_cache_layout", None)
@@ -259,7 +273,8 @@ class FlashCausalLM(Model):
             kv = PagedKVState(
                 sequence_ids=sids, block_table=mgr.block_table_tensor(sids),
                 context_lens=torch.tensor(batch.input_lengths, dtype=torch.int32, device=self.device),
-                slot_mapping=mgr.slot_mapping_for(sids, [0] * B, batch.input_lengths), max_blocks=0)
+                slot_mapping=mgr.slot_mapping_for(sids, [0] * B, batch.input_lengths), max_blocks=0,
+                state_slots=mgr.state_slots_tensor(sids) if hasattr(mgr, "state_slots_tensor") else None)
             batch.past_key_values = kv
             want_all = any(r.details.input_toks for r in batch.requests)
             head_rows = None if want_all else (batch.cu_seqlens[1:] - 1).to(torch.int64)
@@ -288,13 +303,58 @@ class FlashCausalLM(Model):
         batch.max_seqlen += 1
         return generated, input_infos, errs, forward_time_ns
 
+    # --------------------------------------------------------------------------------------------- ragged steps
+    def step_ragged(self, sequence_ids: List[Optional[int]], new_tokens: List[List[int]], logits_rows: Optional[List[int]] = None
+                    ) -> Tuple[List[int], torch.Tensor]:
+        """One forward over a ragged batch: sequence i brings `new_tokens[i]` - a whole prompt, the next portion of one, or one
+        decoded token - after whatever the cache already holds for it (`sequence_ids[i]` None = a new sequence).  Returns the
+        sequence ids and the logits of the token rows `logits_rows` (indices into the concatenated new tokens; None = all).
+        This is the forward that `generate_token` runs with the two regular shapes (all prompts / one token each); chunked
+        prefill and steps that mix portions of prompts with decoding sequences come here directly.  Families whose kernels
+        need the regular shapes do not set `ragged_steps`."""
+        if not getattr(self.model, "ragged_steps", False):
+            raise NotImplementedError(f"{type(self.model).__name__} does not take ragged steps")
+        mgr = self.kv_cache_manager
+        counts = [len(t) for t in new_tokens]
+        if not counts or min(counts) < 1:
+            raise ValueError("every sequence of a step brings at least one token")
+        sids = list(sequence_ids)
+        fresh = [i for i, s in enumerate(sids) if s is None]
+        old = [i for i, s in enumerate(sids) if s is not None]
+        starts = [0 if s is None else mgr.sequence_length(s) for s in sids]
+        if fresh:
+            for i, sid in zip(fresh, mgr.allocate_tokens([counts[i] for i in fresh])):
+                sids[i] = sid
+        if old:
+            try:
+                mgr.allocate_tokens([counts[i] for i in old], [sids[i] for i in old])
+            except BaseException:
+                mgr.free_sequences([sids[i] for i in fresh])
+                raise
+        ends = [s + n for s, n in zip(starts, counts)]
+        dev = self.device
+        flat = torch.tensor([t for toks in new_tokens for t in toks], dtype=torch.int64)
+        pos = torch.cat([torch.arange(s, e, dtype=torch.int64) for s, e in zip(starts, ends)])
+        cu_q = torch.tensor([0] + counts, dtype=torch.int32).cumsum(0, dtype=torch.int32)
+        kv = PagedKVState(sequence_ids=sids, block_table=mgr.block_table_tensor(sids),
+                          context_lens=torch.tensor(ends, dtype=torch.int32).to(dev, non_blocking=True),
+                          slot_mapping=mgr.slot_mapping_for(sids, starts, counts), max_blocks=0,
+                          state_slots=mgr.state_slots_tensor(sids) if hasattr(mgr, "state_slots_tensor") else None)
+        rows = None if logits_rows is None else torch.tensor(logits_rows, dtype=torch.int64).to(dev, non_blocking=True)
+        with self.context_manager():
+            logits, _ = self.model.forward(flat.to(dev, non_blocking=True), pos.to(dev, non_blocking=True), None,
+                                           cu_q.to(dev, non_blocking=True), max(ends), None, kv, None, rows)
+        return sids, logits
+
     def _decode_advance(self, batch) -> None:
         """device bookkeeping at the start of a decode step: position = tokens cached, slot from the block table,
         context += 1 (csrc/kv_alloc.cu)"""
         kv = batch.past_key_values
-        _lib.check(_lib.load().b200_decode_advance(
-            kv.block_table.data_ptr(), kv.block_table.stride(0), kv.context_lens.data_ptr(), batch.position_ids.data_ptr(),
-            kv.slot_mapping.data_ptr(), None, None, len(batch), torch.cuda.current_stream().cuda_stream), "decode_advance")
+        lib = self.kv_cache_manager._lib()
+        if lib.b200_decode_advance(kv.block_table.data_ptr(), kv.block_table.stride(0), kv.context_lens.data_ptr(),
+                                   batch.position_ids.data_ptr(), kv.slot_mapping.data_ptr(), None, None, len(batch),
+                                   torch.cuda.current_stream().cuda_stream) != 0:
+            raise _lib.B200Error(f"decode_advance failed: {lib.b200_last_error().decode()}")
 
     # --------------------------------------------------------------------------------------------- fused greedy decode
     def _can_fuse_greedy(self, batch) -> bool:
@@ -391,7 +451,7 @@ class FlashCausalLM(Model):
         input_ids <- chosen ids, all_input_ids_tensor, cu_seqlens: flash_causal_lm.py:457-458, 533-535 of the reference);
         replayed as ONE CUDA graph from the third step of a stable batch on."""
         kv, B = batch.past_key_values, len(batch)
-        lib = _lib.load()
+        lib = self.kv_cache_manager._lib()
         s = st["step"]
         if use_graph and st["graph"] is not None:
             st["graph"].replay()

@@ -26,7 +26,7 @@ class Model(ABC):
         self.config, self.tokenizer, self.model = engine.get_components()
         self.device = engine.get_device()
         self.dtype = dtype
-        if getattr(self.config, "eos_token_id", None) is not None:
+        if self.tokenizer is not None and getattr(self.config, "eos_token_id", None) is not None:
             self.tokenizer.model_eos_token_id = self.config.eos_token_id
         self.use_position_ids = "position_ids" in inspect.signature(self.model.forward).parameters
         try:

@@ -1,0 +1,214 @@
+"""Tensor-level wrappers over libb200_seq.so: the kernels of the hybrid decoder families (latent attention over a paged latent
+cache, state-space and matrix-memory mixers over fp32 state slots, the row kernels around an fp32 residual stream).
+
+Element type `dtype` is torch.bfloat16 or torch.float32 (weights, activations between projections, cache pages); statistics,
+soft-max, recurrences, states and the residual stream are fp32 in both.  CUDA tensors only; there is no eager fallback.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _dt(t) -> int:
+    d = t if isinstance(t, torch.dtype) else t.dtype
+    if d not in _DT:
+        raise _lib.B200Error(f"element type {d}: the hybrid-family kernels take bfloat16 or float32")
+    return _DT[d]
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.B200Error("expected CUDA tensors (the B200 path has no CPU fallback)")
+
+
+@dataclass
+class RaggedStep:
+    """Index tensors of one step over a ragged batch: sequence b brings the token rows cu_q[b] .. cu_q[b+1] at consecutive
+    positions position_ids[row]; whether that is a prompt, a portion of one or one decoded token makes no difference."""
+    T: int
+    B: int
+    position_ids: torch.Tensor   # [T] int64
+    cu_q: torch.Tensor           # [B + 1] int32
+    seq_of_token: torch.Tensor   # [T] int32
+    slot_mapping: torch.Tensor   # [T] int64: cache row of each token (block * page + offset)
+    block_table: torch.Tensor    # [B, max_blocks] int32
+    state_slots: Optional[torch.Tensor]  # [B] int32
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M, K] (any row stride) @ w [N, K]^T -> [M, N]; fp32 accumulation in ascending k."""
+    _cuda(x, w, bias)
+    assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
+    assert out.stride(1) == 1
+    _lib.check_seq(_lib.load_seq().b200_seq_linear(_ptr(x), _dt(x), x.stride(0), 0, _ptr(w), _dt(w), w.stride(0), 0, _ptr(bias), _ptr(out),
+                                                   _dt(out), out.stride(0), 0, M, N, K, 1, _stream()), "seq_linear")
+    return out
+
+
+def linear_per_head(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """x [M, Z, K], w [Z, N, K], out [M, Z, N] (all may be slices with a wider last-but-one stride): out[:, z] = x[:, z] @ w[z]^T."""
+    _cuda(x, w, out)
+    M, Z, K = x.shape
+    N = w.shape[1]
+    assert w.shape == (Z, N, K) and out.shape == (M, Z, N) and x.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1
+    _lib.check_seq(_lib.load_seq().b200_seq_linear(_ptr(x), _dt(x), x.stride(0), x.stride(1), _ptr(w), _dt(w), w.stride(1), w.stride(0), None,
+                                                   _ptr(out), _dt(out), out.stride(0), out.stride(1), M, N, K, Z, _stream()), "seq_linear")
+    return out
+
+
+def embed_scale(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    """-> fp32 [T, W] = table[ids] * scale (the residual stream starts here)."""
+    _cuda(table, ids)
+    assert ids.dtype == torch.int64 and table.is_contiguous()
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_embed_scale(_ptr(table), _dt(table), _ptr(ids), float(scale), _ptr(out), ids.shape[0],
+                                                        table.shape[1], table.shape[0], _stream()), "seq_embed_scale")
+    return out
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float) -> torch.Tensor:
+    """LayerNorm with weight and bias of a contiguous [T, W] tensor (fp32 stream or an activation); result has w's type."""
+    _cuda(x, w, b)
+    assert x.is_contiguous()
+    out = torch.empty(x.shape, dtype=w.dtype, device=x.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_layernorm(_ptr(x), _dt(x), _ptr(w), _ptr(b), _dt(w), _ptr(out), None, x.shape[0], x.shape[1],
+                                                      float(eps), _stream()), "seq_layernorm")
+    return out
+
+
+def layernorm_into_residual(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, residual: torch.Tensor) -> None:
+    """residual (fp32, in place) += LayerNorm(x) * w + b."""
+    _cuda(x, w, b, residual)
+    assert x.is_contiguous() and residual.is_contiguous() and residual.dtype == torch.float32 and x.shape == residual.shape
+    _lib.check_seq(_lib.load_seq().b200_seq_layernorm(_ptr(x), _dt(x), _ptr(w), _ptr(b), _dt(w), None, _ptr(residual), x.shape[0],
+                                                      x.shape[1], float(eps), _stream()), "seq_layernorm")
+
+
+GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER = 0, 1, 2
+
+
+def group_rmsnorm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], groups: int, eps: float, out_dtype: torch.dtype,
+                       gate: Optional[torch.Tensor] = None, gate_kind: int = GATE_NONE) -> torch.Tensor:
+    """x, gate: fp32 [T, C] column slices.  Per group of C / groups columns: v / sqrt(mean(v^2) + eps) * weight, with the gate
+    multiplied in before the statistics (SiLU) or after the weight (sigmoid).  groups == 0: no normalisation."""
+    _cuda(x, weight, gate)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and (gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1))
+    T, C = x.shape
+    n = C // groups if groups > 0 else C
+    assert groups == 0 or n * groups == C
+    out = torch.empty(T, C, dtype=out_dtype, device=x.device)
+    w_dt = _dt(weight) if weight is not None else _dt(out_dtype)
+    _lib.check_seq(_lib.load_seq().b200_seq_group_rmsnorm_gate(
+        _ptr(x), x.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, gate_kind, _ptr(weight), w_dt, groups, n, float(eps),
+        _ptr(out), _dt(out), out.stride(0), T, _stream()), "seq_group_rmsnorm_gate")
+    return out
+
+
+def ff_clamped_gate(gate_up: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """[T, 2F] = [g | u] -> [T, F]: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    _cuda(gate_up)
+    assert gate_up.is_contiguous()
+    T, F2 = gate_up.shape
+    out = torch.empty(T, F2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_ff_clamped_gate(_ptr(gate_up), _ptr(out), _dt(gate_up), T, F2 // 2, float(limit), float(alpha),
+                                                            _stream()), "seq_ff_clamped_gate")
+    return out
+
+
+def token_side(residual: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int, dim: int, w_gate: torch.Tensor,
+               w_proj: torch.Tensor, norm_w: torch.Tensor, eps: float) -> None:
+    """residual (fp32, in place) += unit_rms(w_proj (gelu_tanh(w_gate x) * table[id, col0:col0+dim])) * norm_w."""
+    _cuda(residual, ids, table, w_gate, w_proj, norm_w)
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and w_gate.is_contiguous() and w_proj.is_contiguous()
+    T, W = residual.shape
+    _lib.check_seq(_lib.load_seq().b200_seq_token_side(_ptr(residual), _ptr(ids), _ptr(table), table.stride(0), col0, dim, table.shape[0],
+                                                       _ptr(w_gate), _ptr(w_proj), _ptr(norm_w), _dt(table), T, W, float(eps), _stream()),
+                   "seq_token_side")
+
+
+def latent_prepare(down: torch.Tensor, col_c: int, col_kr: int, q: torch.Tensor, q_head_stride: int, q_rot_off: int,
+                   cnorm_w: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, step: RaggedStep, cache: torch.Tensor, q_abs: torch.Tensor,
+                   H: int, R: int, r: int, rot_dims: int, eps: float) -> None:
+    """Writes each token's cache row [unit_rms(latent) * w | rotated key part] and the rotated query parts q_abs[:, :, R:]."""
+    _cuda(down, q, cache, q_abs)
+    assert down.dtype == torch.float32 and q.dtype == torch.float32 and q_abs.dtype == torch.float32 and cos.dtype == torch.float32
+    assert q_abs.is_contiguous() and cache.is_contiguous() and cos.is_contiguous() and sin.is_contiguous()
+    _lib.check_seq(_lib.load_seq().b200_seq_latent_prepare(
+        _ptr(down), down.stride(0), col_c, col_kr, _ptr(q), q.stride(0), q_head_stride, q_rot_off, _ptr(cnorm_w), _ptr(cos), _ptr(sin),
+        _ptr(step.position_ids), _ptr(step.slot_mapping), _ptr(cache), _dt(cache), _ptr(q_abs), step.T, H, R, r, rot_dims, float(eps),
+        _stream()), "seq_latent_prepare")
+
+
+def latent_attn(q_abs: torch.Tensor, cache: torch.Tensor, step: RaggedStep, R: int, r: int, window: int, scale: float) -> torch.Tensor:
+    """q_abs fp32 [T, H, R + r], cache [blocks, page, R + r] -> fp32 [T, H, R]: soft-max attention of every token over the cache
+    rows of its own sequence at positions (p - window, p], in latent space."""
+    _cuda(q_abs, cache)
+    T, H, D = q_abs.shape
+    assert D == R + r and cache.shape[-1] == D and q_abs.is_contiguous() and cache.is_contiguous()
+    out = torch.empty(T, H, R, dtype=torch.float32, device=q_abs.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_latent_attn(
+        _ptr(q_abs), _ptr(cache), _dt(cache), _ptr(step.block_table), step.block_table.stride(0), _ptr(step.seq_of_token),
+        _ptr(step.position_ids), _ptr(out), T, H, R, r, int(window), float(scale), cache.shape[1], _stream()), "seq_latent_attn")
+    return out
+
+
+def causal_conv_silu(u: torch.Tensor, col0: int, channels: int, w: torch.Tensor, bias: torch.Tensor, conv_state: torch.Tensor,
+                     step: RaggedStep) -> torch.Tensor:
+    """SiLU(depth-wise causal convolution) of the columns [col0, col0 + channels) of u (fp32); conv_state [slots, taps - 1, channels]
+    supplies the inputs before this step's first token and is advanced to the sequence's last taps - 1 inputs."""
+    _cuda(u, w, bias, conv_state)
+    assert u.dtype == torch.float32 and conv_state.dtype == torch.float32 and w.is_contiguous() and conv_state.is_contiguous()
+    taps = w.shape[1]
+    out = torch.empty(step.T, channels, dtype=torch.float32, device=u.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_causal_conv_silu(
+        _ptr(u), u.stride(0), col0, channels, taps, _ptr(w), _ptr(bias), _dt(w), _ptr(conv_state), _ptr(step.state_slots),
+        _ptr(step.seq_of_token), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(out), step.T, step.B, _stream()), "seq_causal_conv_silu")
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, col_x: int, col_B: int, col_C: int, dt_raw: torch.Tensor, col_dt: int, dt_bias: torch.Tensor,
+             A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, step: RaggedStep, H: int, P: int, N: int, groups: int) -> torch.Tensor:
+    """-> y fp32 [T, H * P]; state fp32 [slots, H, N, P] advanced in place."""
+    _cuda(xbc, dt_raw, state)
+    assert xbc.dtype == torch.float32 and dt_raw.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
+    y = torch.empty(step.T, H * P, dtype=torch.float32, device=xbc.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_ssm_scan(
+        _ptr(xbc), xbc.stride(0), col_x, col_B, col_C, _ptr(dt_raw), dt_raw.stride(0), col_dt, _ptr(dt_bias), _ptr(A_log), _ptr(D),
+        _dt(dt_bias), _ptr(state), _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(y), y.stride(0), step.B, H, P, N,
+        groups, _stream()), "seq_ssm_scan")
+    return y
+
+
+def mlstm_scan(proj: torch.Tensor, col_q: int, col_k: int, col_v: int, col_i: int, col_f: int, i_bias: torch.Tensor, f_bias: torch.Tensor,
+               cap: float, q_scale: float, S: torch.Tensor, n: torch.Tensor, m: torch.Tensor, step: RaggedStep, H: int, dk: int, dv: int
+               ) -> torch.Tensor:
+    """-> y fp32 [T, H * dv]; S [slots, H, dk, dv], n [slots, H, dk], m [slots, H] (fp32) advanced in place."""
+    _cuda(proj, S, n, m)
+    assert proj.dtype == torch.float32 and S.is_contiguous() and n.is_contiguous() and m.is_contiguous()
+    y = torch.empty(step.T, H * dv, dtype=torch.float32, device=proj.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_mlstm_scan(
+        _ptr(proj), proj.stride(0), col_q, col_k, col_v, col_i, col_f, _ptr(i_bias), _ptr(f_bias), _dt(i_bias), float(cap), float(q_scale),
+        _ptr(S), _ptr(n), _ptr(m), _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(y), y.stride(0), step.B, H, dk, dv,
+        _stream()), "seq_mlstm_scan")
+    return y

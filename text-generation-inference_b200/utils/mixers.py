@@ -1,0 +1,182 @@
+"""Sequence mixers beyond plain multi-head attention, each with its constants as constructor arguments so that any decoder
+family can compose them: latent attention over a paged latent cache (sliding window, rotary part with optional YaRN frequency
+scaling), the selective state-space mixer (Mamba-2 form) and the matrix-memory mixer (mLSTM).
+
+A mixer declares what it keeps per sequence (`cache_spec`): a row of the paged cache per token, or fp32 state tensors in a
+state slot.  `forward(h, step, store)` takes the normed hidden states of a ragged step (ops_seq.RaggedStep: any mix of whole
+prompts, portions of prompts and single decoded tokens) and the layer's store from the cache manager (utils/paged.py
+`HybridCacheManager`).  Kernels: csrc/seq_*.cu through ops_seq.py.  Projections accumulate in fp32; soft-max, norms, gates of
+the recurrences and the states are fp32 whatever the element type.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+from torch import nn
+
+from .. import ops_seq as ops
+from .paged import LayerCacheSpec
+
+
+def _need_single_rank(weights, what: str):
+    if weights.process_group.size() != 1:
+        raise NotImplementedError(f"{what} is not sharded: run it on one rank")
+
+
+class ScaledRotaryTables:
+    """cos / sin of position * frequency for interleaved-pair rotation, fp32 [positions, dims / 2], grown on demand.
+    frequency_i = base^(-2i/dims).  With `scaling` = {factor, original, fast, slow} (YaRN): pairs that turn more than `fast`
+    times over `original` positions keep their frequency, pairs that turn fewer than `slow` times are slowed by `factor`, a
+    linear ramp over the pair index in between; cos and sin are multiplied by 0.1 ln(factor) + 1."""
+
+    def __init__(self, dims: int, base: float, scaling: Optional[dict] = None):
+        if dims % 2:
+            raise ValueError("rotary dims must be even")
+        self.dims, self.base, self.scaling = int(dims), float(base), scaling
+        self._cos = self._sin = None
+
+    def frequencies(self) -> torch.Tensor:
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        freq = self.base ** (-2.0 * i / self.dims)
+        sc = self.scaling
+        if sc:
+            def pair_turning(turns: float) -> float:  # (fractional) pair index that makes `turns` turns over the original length
+                return self.dims * math.log(float(sc["original"]) / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(pair_turning(float(sc["fast"]))), 0)
+            hi = min(math.ceil(pair_turning(float(sc["slow"]))), self.dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            freq = freq / float(sc["factor"]) * ramp + freq * (1.0 - ramp)
+        return freq
+
+    def amplitude(self) -> float:
+        return 0.1 * math.log(float(self.scaling["factor"])) + 1.0 if self.scaling else 1.0
+
+    def tables(self, n_pos: int, device):
+        if self._cos is None or self._cos.shape[0] < n_pos or self._cos.device != torch.device(device):
+            n = max(256, 1 << (max(int(n_pos), 1) - 1).bit_length())
+            ang = torch.arange(n, dtype=torch.float64)[:, None] * self.frequencies()[None, :]
+            amp = self.amplitude()
+            self._cos = (torch.cos(ang) * amp).to(torch.float32).to(device).contiguous()
+            self._sin = (torch.sin(ang) * amp).to(torch.float32).to(device).contiguous()
+        return self._cos, self._sin
+
+
+class LatentAttention(nn.Module):
+    """Multi-head attention whose keys and values are up-projections of one latent per token (rank `kv_rank`) plus one rotated
+    key part (`rot_dim`) shared by all heads; queries go through a latent of rank `q_rank`.  Only the normalised latent and the
+    rotated key part are cached: `kv_rank + rot_dim` elements per token and layer.  The kernels work in the absorbed form (the
+    key up-projection is applied to the query, the value up-projection to the attention output), for prompts and decoding alike.
+    Tensors under `prefix`: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g (sigmoid gate on the concatenated heads), o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, scale: float,
+                 window: Optional[int], rotary: ScaledRotaryTables, eps: float):
+        super().__init__()
+        _need_single_rank(weights, "LatentAttention")
+        self.H, self.d, self.r, self.dv, self.R, self.Q = heads, dim, rot_dim, vdim, kv_rank, q_rank
+        self.scale, self.window, self.rotary, self.eps = float(scale), int(window or 0), rotary, float(eps)
+        if rotary.dims > rot_dim:
+            raise ValueError("rotary dims exceed the rotated part")
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_in = torch.cat([get("dq"), get("dkv"), get("g")], 0).contiguous()          # -> [q latent | kv latent | key part | gate]
+        self.dq_norm, self.dkv_norm = get("dq.norm"), get("dkv.norm")
+        self.w_uq = get("uq").contiguous()                                               # rows head by head: [dim plain | rot_dim rotated]
+        self.w_uk_t = get("uk").view(heads, dim, kv_rank).transpose(1, 2).contiguous()   # [H, R, d]: q~ = Wuk_h^T q_plain
+        self.w_uv = get("uv").view(heads, vdim, kv_rank).contiguous()
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="paged", row_width=self.R + self.r)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, store, max_s: int) -> torch.Tensor:
+        H, d, r, dv, R, Q = self.H, self.d, self.r, self.dv, self.R, self.Q
+        T = step.T
+        down = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        cq = ops.group_rmsnorm_gate(down[:, :Q], self.dq_norm, 1, self.eps, self.dtype)
+        q = ops.linear(cq, self.w_uq, out_dtype=torch.float32)
+        q_abs = torch.empty(T, H, R + r, dtype=torch.float32, device=h.device)
+        cos, sin = self.rotary.tables(max_s, h.device)
+        ops.latent_prepare(down, Q, Q + R, q, d + r, d, self.dkv_norm, cos, sin, step, store, q_abs, H, R, r, self.rotary.dims, self.eps)
+        ops.linear_per_head(q.view(T, H, d + r)[:, :, :d], self.w_uk_t, q_abs[:, :, :R])
+        o_lat = ops.latent_attn(q_abs, store, step, R, r, self.window, self.scale)
+        o = torch.empty(T, H, dv, dtype=torch.float32, device=h.device)
+        ops.linear_per_head(o_lat, self.w_uv, o)
+        gated = ops.group_rmsnorm_gate(o.view(T, H * dv), None, 0, self.eps, self.dtype, gate=down[:, Q + R + r:],
+                                       gate_kind=ops.GATE_SIGMOID_AFTER)
+        return ops.linear(gated, self.w_o)
+
+
+class Mamba2Mixer(nn.Module):
+    """Selective state-space mixer: in-projection [z | x | B | C | dt], depth-wise causal convolution + SiLU over [x | B | C],
+    per head S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, then y * SiLU(z), RMS norm in `norm_groups` parts, out-projection.
+    State per sequence: S [heads, state, vdim] and the last conv - 1 convolution inputs, both fp32.
+    Tensors under `prefix`: in, conv, conv.b, dt_bias, A_log, D, norm, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, vdim: int, state: int, groups: int, conv: int, norm_groups: int, eps: float):
+        super().__init__()
+        _need_single_rank(weights, "Mamba2Mixer")
+        self.H, self.P, self.N, self.G, self.taps, self.norm_groups, self.eps = heads, vdim, state, groups, conv, norm_groups, float(eps)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}").contiguous()  # noqa: E731
+        self.w_in, self.conv_w, self.conv_b = get("in"), get("conv"), get("conv.b")
+        self.dt_bias, self.A_log, self.D, self.norm_w, self.w_o = get("dt_bias"), get("A_log"), get("D"), get("norm"), get("o")
+        self.inner = heads * vdim
+        self.channels = self.inner + 2 * groups * state
+        self.dtype = self.w_o.dtype
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state={"S": (self.H, self.N, self.P), "conv": (max(self.taps - 1, 1), self.channels)})
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, store: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        inner, GN = self.inner, self.G * self.N
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        xbc = ops.causal_conv_silu(u, inner, self.channels, self.conv_w, self.conv_b, store["conv"], step)
+        y = ops.ssm_scan(xbc, 0, inner, inner + GN, u, 2 * inner + 2 * GN, self.dt_bias, self.A_log, self.D, store["S"], step, self.H, self.P,
+                         self.N, self.G)
+        gated = ops.group_rmsnorm_gate(y, self.norm_w, self.norm_groups, self.eps, self.dtype, gate=u[:, :inner], gate_kind=ops.GATE_SILU_BEFORE)
+        return ops.linear(gated, self.w_o)
+
+
+class MLSTMMixer(nn.Module):
+    """Matrix-memory mixer: per head a [dim, vdim] memory S, a normaliser n and a running maximum m (from 0) of the log gates;
+    log input gate cap tanh(./cap), log forget gate logsigmoid(cap tanh(./cap)); read-out S^T q / (max(|n.q|, e^-m) + 1e-6) with
+    q scaled by dim^-1/2, per-head unit-RMS, weight, sigmoid output gate, out-projection.  State fp32.
+    Tensors under `prefix`: q, k, v, g, i, i.b, f, f.b, norm, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, dim: int, vdim: int, gate_cap: float, eps: float):
+        super().__init__()
+        _need_single_rank(weights, "MLSTMMixer")
+        self.H, self.d, self.dv, self.cap, self.eps = heads, dim, vdim, float(gate_cap), float(eps)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}").contiguous()  # noqa: E731
+        self.w_in = torch.cat([get("q"), get("k"), get("v"), get("g"), get("i"), get("f")], 0).contiguous()
+        self.i_b, self.f_b, self.norm_w, self.w_o = get("i.b"), get("f.b"), get("norm"), get("o")
+        self.dtype = self.w_o.dtype
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state={"S": (self.H, self.d, self.dv), "n": (self.H, self.d), "m": (self.H,)})
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, store: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        H, d, dv = self.H, self.d, self.dv
+        qk, vg = 2 * H * d, 2 * H * dv
+        proj = ops.linear(h, self.w_in, out_dtype=torch.float32)  # [q | k | v | g | i | f]
+        y = ops.mlstm_scan(proj, 0, H * d, qk, qk + vg, qk + vg + H, self.i_b, self.f_b, self.cap, d ** -0.5, store["S"], store["n"],
+                           store["m"], step, H, d, dv)
+        gated = ops.group_rmsnorm_gate(y, self.norm_w, H, self.eps, self.dtype, gate=proj[:, qk + H * dv:qk + vg],
+                                       gate_kind=ops.GATE_SIGMOID_AFTER)
+        return ops.linear(gated, self.w_o)
+
+
+class ClampedGatedMLP(nn.Module):
+    """down(g' * sigmoid(alpha g') * (u' + 1)) with g' = min(gate(x), limit), u' = clamp(up(x), -limit, limit).
+    Tensors under `prefix`: gate, up, down."""
+
+    def __init__(self, prefix: str, weights, *, limit: float, alpha: float = 1.702):
+        super().__init__()
+        _need_single_rank(weights, "ClampedGatedMLP")
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.w_gate_up = torch.cat([weights.get_tensor(f"{prefix}.gate"), weights.get_tensor(f"{prefix}.up")], 0).contiguous()
+        self.w_down = weights.get_tensor(f"{prefix}.down").contiguous()
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.linear(ops.ff_clamped_gate(ops.linear(h, self.w_gate_up), self.limit, self.alpha), self.w_down)

@@ -33,6 +33,7 @@ class PagedKVState:
     context_lens: torch.Tensor  # [B] int32: tokens cached (decode: advanced by the step's bookkeeping kernel)
     slot_mapping: torch.Tensor  # [T] int64 for the tokens of the current step
     max_blocks: int
+    state_slots: Optional[torch.Tensor] = None  # [B] int32: recurrent-state slot of each sequence (HybridCacheManager only)
 
 
 @dataclass
@@ -81,7 +82,14 @@ class PagedKVCacheManager:
         # zero-filled: masked tail slots must be finite (attn_decode.cu multiplies them by p = 0)
         self.pool = torch.zeros(num_layers, 2, self.total_num_gpu_blocks, self.kv_heads, block_size, self.head_dim,
                                 dtype=dtype, device=self.device)
-        self._alloc = _lib.load().b200_kv_alloc_create(self.total_num_gpu_blocks)
+        self._init_block_bookkeeping()
+
+    def _lib(self):
+        """the library that holds the block allocator (a subclass served by another library overrides this)"""
+        return _lib.load()
+
+    def _init_block_bookkeeping(self) -> None:
+        self._alloc = self._lib().b200_kv_alloc_create(self.total_num_gpu_blocks)
         if not self._alloc:
             raise _lib.B200Error("kv_alloc_create failed")
         self._blocks: Dict[int, List[int]] = {}
@@ -97,12 +105,12 @@ class PagedKVCacheManager:
 
     @property
     def free_blocks(self) -> int:
-        return int(_lib.load().b200_kv_alloc_num_free(self._alloc))
+        return int(self._lib().b200_kv_alloc_num_free(self._alloc))
 
     def __del__(self):
         try:
             if getattr(self, "_alloc", None):
-                _lib.load().b200_kv_alloc_destroy(self._alloc)
+                self._lib().b200_kv_alloc_destroy(self._alloc)
                 self._alloc = None
         except Exception:
             pass
@@ -124,7 +132,7 @@ class PagedKVCacheManager:
         if n == 0:
             return []
         buf = (ctypes.c_int32 * n)()
-        st = _lib.load().b200_kv_alloc_take(self._alloc, n, buf)
+        st = self._lib().b200_kv_alloc_take(self._alloc, n, buf)
         if st != 0:
             raise OutOfBlocks(f"KV cache exhausted: need {n} blocks, {self.free_blocks} free")
         return list(buf)
@@ -141,7 +149,8 @@ class PagedKVCacheManager:
                 self._refs[b] = n
         if free:
             buf = (ctypes.c_int32 * len(free))(*free)
-            _lib.check(_lib.load().b200_kv_alloc_release(self._alloc, buf, len(free)), "kv_alloc_release")
+            if self._lib().b200_kv_alloc_release(self._alloc, buf, len(free)) != 0:
+                raise _lib.B200Error(f"kv_alloc_release failed: {self._lib().b200_last_error().decode()}")
 
     def blocks_needed(self, num_tokens: int) -> int:
         return (num_tokens + self.block_size - 1) // self.block_size
@@ -274,6 +283,98 @@ class PagedKVCacheManager:
             pos = torch.arange(st, st + n, dtype=torch.int64)
             out.append(blocks[pos // self.block_size] * self.block_size + pos % self.block_size)
         return torch.cat(out).to(self.device, non_blocking=True) if out else torch.empty(0, dtype=torch.int64, device=self.device)
+
+
+@dataclass
+class LayerCacheSpec:
+    """What one layer keeps per sequence: "paged" = `row_width` elements per token in the block pool; "state" = fp32 tensors of
+    the given shapes in the sequence's state slot; "none" = nothing."""
+    kind: str = "none"
+    row_width: int = 0
+    state: Optional[Dict[str, tuple]] = None
+
+
+class HybridCacheManager(PagedKVCacheManager):
+    """Block pool + state slots for decoders that mix attention layers with recurrent layers.
+
+    Same block bookkeeping as the KV manager (allocator, per-sequence block lists, reference counts, block tables, slot mapping),
+    but every layer says what it stores: a paged layer gets its own pool [num_blocks, block_size, row_width] of the model's element
+    type (one row per token, no head dimension: e.g. the latent + rotated key part of latent attention), a state layer gets fp32
+    tensors [num_state_slots, *shape].  A sequence takes one state slot when it is created and gives it back, with its blocks,
+    in `free_sequences`; slots are not cleared on reuse: the kernels start a sequence at position 0 from a zero state without
+    reading the slot."""
+
+    def __init__(self, layers: List[LayerCacheSpec], dtype: torch.dtype, device, total_num_gpu_blocks: int, num_state_slots: int,
+                 block_size: int = BLOCK_SIZE):
+        self.block_size = block_size
+        self.layer_specs = list(layers)
+        self.num_layers = len(self.layer_specs)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.total_num_gpu_blocks = int(total_num_gpu_blocks)
+        self.num_state_slots = int(num_state_slots)
+        self.kv_heads, self.head_dim = 1, 0
+        self.pool = None
+        self.pages: List[Optional[torch.Tensor]] = []
+        self.states: List[Optional[Dict[str, torch.Tensor]]] = []
+        for spec in self.layer_specs:
+            if spec.kind == "paged":
+                self.pages.append(torch.zeros(self.total_num_gpu_blocks, block_size, spec.row_width, dtype=dtype, device=self.device))
+                self.states.append(None)
+            elif spec.kind == "state":
+                self.pages.append(None)
+                self.states.append({name: torch.zeros(self.num_state_slots, *shape, dtype=torch.float32, device=self.device)
+                                    for name, shape in spec.state.items()})
+            else:
+                self.pages.append(None)
+                self.states.append(None)
+        self._free_slots: List[int] = list(range(self.num_state_slots - 1, -1, -1))  # slot 0 is handed out first
+        self._slot_of: Dict[int, int] = {}
+        self._init_block_bookkeeping()
+
+    def _lib(self):
+        return _lib.load_seq()
+
+    def layer_store(self, layer: int):
+        """the layer's pool (paged), its dict of state tensors (state) or None"""
+        return self.pages[layer] if self.pages[layer] is not None else self.states[layer]
+
+    def block_bytes(self) -> int:
+        return sum(p.shape[1] * p.shape[2] * p.element_size() for p in self.pages if p is not None)
+
+    def state_bytes_per_slot(self) -> int:
+        return sum(t[0].numel() * 4 for st in self.states if st for t in st.values())
+
+    @property
+    def free_state_slots(self) -> int:
+        return len(self._free_slots)
+
+    def allocate_tokens(self, num_tokens_per_sequence: List[int], sequence_ids: Optional[List[int]] = None,
+                        reserve_tokens: Optional[List[int]] = None) -> List[int]:
+        new = sequence_ids is None
+        if new and len(num_tokens_per_sequence) > len(self._free_slots):
+            raise OutOfBlocks(f"state slots exhausted: need {len(num_tokens_per_sequence)}, {len(self._free_slots)} free")
+        ids = super().allocate_tokens(num_tokens_per_sequence, sequence_ids, reserve_tokens)
+        if new:
+            for sid in ids:
+                self._slot_of[sid] = self._free_slots.pop()
+        return ids
+
+    def free_sequences(self, sequence_ids: List[int], recursive: bool = False) -> None:
+        for sid in sequence_ids:
+            slot = self._slot_of.pop(sid, None)
+            if slot is not None:
+                self._free_slots.append(slot)
+        super().free_sequences(sequence_ids, recursive)
+
+    def add_child_sequences(self, parent_sequence_id: int, num_children: int) -> List[int]:
+        raise NotImplementedError("speculative child sequences would have to copy the parent's recurrent state")
+
+    def state_slot(self, sid: int) -> int:
+        return self._slot_of[sid]
+
+    def state_slots_tensor(self, sequence_ids: List[int]) -> torch.Tensor:
+        return torch.tensor([self._slot_of[s] for s in sequence_ids], dtype=torch.int32).to(self.device, non_blocking=True)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
