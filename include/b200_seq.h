@@ -1,0 +1,70 @@
+/* C ABI of libb200_seq.so: kernels of the hybrid decoder families (latent attention over a paged latent cache, state-space
+ * and matrix-memory mixers over fp32 state slots, row kernels around an fp32 residual stream).
+ *
+ * Conventions as in b200_tgis.h: plain device pointers + sizes + a cudaStream_t (void*), status-code return (0 = ok, the
+ * message through b200_last_error()), no allocation, enqueue-only.  Element types are passed as codes: 0 = bfloat16,
+ * 1 = float32.  Everything called "state", "residual", soft-max and norm statistics is fp32 whatever the element type.
+ * The library also exports b200_last_error, b200_cuda_peek_error, b200_launch_count, b200_kv_alloc_* and b200_decode_advance
+ * with the signatures b200_tgis.h gives them.
+ *
+ * A ragged step: T token rows of B sequences; sequence b owns rows cu_q[b] .. cu_q[b+1], at consecutive positions
+ * position_ids[row]; seq_of_token[row] = b; slot_mapping[row] = cache row (block * page + offset); state_slots[b] = the
+ * sequence's recurrent-state slot.  A sequence whose first row of the step is at position 0 starts from a zero state.
+ */
+#ifndef B200_SEQ_H
+#define B200_SEQ_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_DT_BF16 0
+#define B200_DT_F32 1
+
+/* C[z][m][n] = sum_k A[z][m][k] W[z][n][k] (+ bias[n]); fp32 accumulation in ascending k; strides in elements */
+int b200_seq_linear(const void* A, int a_dt, int64_t lda, int64_t strideA, const void* W, int w_dt, int64_t ldw, int64_t strideW,
+                    const void* bias, void* C, int c_dt, int64_t ldc, int64_t strideC, int64_t M, int64_t N, int64_t K, int64_t Z,
+                    void* stream);
+/* out[t] = table[ids[t]] * scale, fp32 */
+int b200_seq_embed_scale(const void* table, int dt, const int64_t* ids, float scale, float* out, int64_t T, int64_t W, int64_t V,
+                         void* stream);
+/* LayerNorm with weight and bias of rows of type x_dt; resid == NULL: out (type dt) = LN(x), else resid (fp32) += LN(x) */
+int b200_seq_layernorm(const void* x, int x_dt, const void* w, const void* b, int dt, void* out, float* resid, int64_t T, int64_t W,
+                       float eps, void* stream);
+/* per group of n columns: v / sqrt(mean v^2 + eps) * w; gate_kind 0 none, 1 SiLU(gate) before the statistics, 2 sigmoid(gate)
+ * after the weight; groups == 0: gate only */
+int b200_seq_group_rmsnorm_gate(const float* x, int64_t ldx, const float* gate, int64_t ldg, int gate_kind, const void* w, int w_dt,
+                                int groups, int n, float eps, void* out, int out_dt, int64_t ldo, int64_t T, void* stream);
+/* [g | u] rows -> min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) + 1) */
+int b200_seq_ff_clamped_gate(const void* gu, void* out, int dt, int64_t rows, int64_t F, float limit, float alpha, void* stream);
+/* resid += unit_rms(Wp (gelu_tanh(Wg resid) * table[id, col0 : col0 + dim])) * nw */
+int b200_seq_token_side(float* resid, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V,
+                        const void* Wg, const void* Wp, const void* nw, int dt, int64_t T, int64_t W, float eps, void* stream);
+/* cache row of every token = [unit_rms(latent) * w | rotated key part]; q_abs[:, :, R:] = rotated query parts */
+int b200_seq_latent_prepare(const float* down, int64_t ld_down, int col_c, int col_kr, const float* q, int64_t ld_q, int q_head_stride,
+                            int q_rot_off, const void* cnorm_w, const float* cos_t, const float* sin_t, const int64_t* position_ids,
+                            const int64_t* slot_mapping, void* cache, int dt, float* q_abs, int64_t T, int H, int R, int r, int rot_dims,
+                            float eps, void* stream);
+/* out[t, h, :R] = sum_j softmax_j((q_abs[t, h] . cache_row(j)) * scale) cache_row(j)[:R], j over (p - window, p] of t's sequence */
+int b200_seq_latent_attn(const float* q_abs, const void* cache, int dt, const int32_t* block_table, int64_t bt_stride,
+                         const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int R, int r, int window,
+                         float scale, int page, void* stream);
+/* SiLU(depth-wise causal convolution) of columns [col0, col0 + C) of u; conv_state [slots, taps - 1, C] read and advanced */
+int b200_seq_causal_conv_silu(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt,
+                              float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
+                              const int64_t* position_ids, float* out, int64_t T, int B, void* stream);
+/* S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, dt = softplus(raw + bias); state [slots, H, N, P] */
+int b200_seq_ssm_scan(const float* xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* dt_raw, int64_t ld_dt, int col_dt,
+                      const void* dt_bias, const void* A_log, const void* Dskip, int dt, float* state, const int32_t* state_slots,
+                      const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int P, int N, int groups,
+                      void* stream);
+/* matrix memory with exponential gating and a running maximum from 0; S [slots, H, dk, dv], n [slots, H, dk], m [slots, H] */
+int b200_seq_mlstm_scan(const float* proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const void* i_bias,
+                        const void* f_bias, int dt, float cap, float q_scale, float* S_state, float* n_state, float* m_state,
+                        const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H,
+                        int dk, int dv, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
