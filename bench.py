@@ -54,6 +54,8 @@ WORKLOADS = {
     "llama3-70b-gptq": ("llama-3-70b", "gptq", 128, 512, 1024),  # steady-state sibling of config[4]; needs --gpus 2 or more
     "pythia-12b-fp16": ("pythia-12b", None, 64, 1024, 2048),  # GPT-NeoX, the second flash family (parallel residual, partial rotary)
     "tiny-neox": ("tiny-neox", None, 4, 32, 256),
+    "neox-w2048": ("neox-w2048", None, 32, 1024, 1088),  # equal-size partners of --hybrid-compare (3 layers of a real model's widths)
+    "neox-w4096": ("neox-w4096", None, 32, 1024, 1088),
     "tinyllama-fp16": ("tinyllama-1.1b", None, 32, 512, 1024),
     "tiny-test": ("tiny-test", None, 4, 32, 256),
 }
@@ -663,6 +665,211 @@ def run_gpu(args, workload):
     return 0
 
 
+# ------------------------------------------------------------------------------------------------ --hybrid-compare
+def _timed_ops(module, names, log):
+    """wraps module-level op functions with a CUDA-event pair per call; log gets (name, start, end) triples"""
+    import torch
+    saved = {}
+    for n in names:
+        fn = getattr(module, n)
+        saved[n] = fn
+
+        def wrapped(*a, __fn=fn, __n=n, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = __fn(*a, **k)
+            e1.record()
+            log.append((__n, e0, e1))
+            return out
+        setattr(module, n, wrapped)
+    return saved
+
+
+def _by_op(log):
+    import torch
+    torch.cuda.synchronize()
+    out = {}
+    for n, e0, e1 in log:
+        out[n] = out.get(n, 0.0) + e0.elapsed_time(e1)
+    return out
+
+
+def run_hybrid_compare(args):
+    """Fetotar (bfloat16) beside GPT-NeoX (fp16) at equal width and depth, random weights: prefill of 4 x 1024 tokens and decode of
+    32 sequences at context 1024.  Per model: tokens/s through the engine's own step (device time by CUDA events, L2 flushed
+    between timed calls) and the device time of every kernel family inside one step; for the kernels that carry a step, achieved
+    FLOP/s or bytes/s against the measured peaks."""
+    import torch
+    import tgis_b200  # noqa: F401
+    from tgis_b200 import ops as ops_f16, ops_seq
+    from tgis_b200.inference_engine import InferenceEngine
+    from tgis_b200.models.custom_modeling.fetotar_modeling import FetotarConfig
+    from tgis_b200.models.flash_causal_lm import FlashCausalLM
+    from tgis_b200.utils.dist import FakeGroup
+    from tgis_b200.utils.synthetic import SyntheticHybridWeights, fetotar_config, make_tokenizer
+
+    pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        pk = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    PB, PL, DB, DL = 4, 1024, 32, 1024
+    K, Wm = max(args.steps // 4, 4), args.warmup
+    results = []
+
+    def timed(fn, n):
+        total = 0.0
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / n
+
+    for width in (2048, 4096):
+        # ---------------------------------------------------------------- the hybrid model
+        raw = fetotar_config(f"fetotar-w{width}")
+        cfg = FetotarConfig(raw)
+        weights = SyntheticHybridWeights(raw, dev, torch.bfloat16, FakeGroup(0, 1))
+        engine = InferenceEngine("<synthetic>", None, torch.bfloat16, None, cfg, None, weights=weights, tokenizer=make_tokenizer(cfg.vocab_size))
+        model = FlashCausalLM("<synthetic>", None, "tgis_native", torch.bfloat16, None, cfg, engine=engine,
+                              num_kv_blocks=(DB + PB) * ((DL + 64) // 16 + 2), num_state_slots=DB + PB)
+        g = torch.Generator().manual_seed(0)
+        prompt = lambda n, L: [torch.randint(4, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(n)]  # noqa: E731
+
+        def prefill_once():
+            sids, _ = model.step_ragged([None] * PB, prompts_p, [PL * (i + 1) - 1 for i in range(PB)])
+            model.kv_cache_manager.free_sequences(sids)
+        prompts_p = prompt(PB, PL)
+        for _ in range(Wm):
+            prefill_once()
+        pre_ms = timed(prefill_once, K)
+        names = [n for n in ("linear", "linear_per_head", "embed_scale", "layernorm", "layernorm_into_residual", "group_rmsnorm_gate",
+                             "ff_clamped_gate", "token_side", "latent_prepare", "latent_attn", "causal_conv_silu", "ssm_scan", "mlstm_scan")]
+        log = []
+        saved = _timed_ops(ops_seq, names, log)
+        prefill_once()
+        pre_ops = _by_op(log)
+        sids, _ = model.step_ragged([None] * DB, prompt(DB, DL), [])
+        nxt = [[7]] * DB
+
+        def decode_once():
+            model.step_ragged(sids, nxt, None)
+        log.clear()
+        for n, fn in saved.items():
+            setattr(ops_seq, n, fn)
+        for _ in range(Wm):
+            decode_once()
+        dec_ms = timed(decode_once, K)
+        saved = _timed_ops(ops_seq, names, log)
+        decode_once()
+        dec_ops = _by_op(log)
+        for n, fn in saved.items():
+            setattr(ops_seq, n, fn)
+        model.kv_cache_manager.free_sequences(sids)
+        la, ss, ml = raw["layers"][1]["mixer"], raw["layers"][2]["mixer"], raw["layers"][0]["mixer"]
+        D, R, H = la["kv_rank"] + la["rot_dim"], la["kv_rank"], la["heads"]
+        attn_flops = PB * (PL * (PL + 1) // 2) * H * (D + R) * 2
+        ctx = DL + Wm + K + 2
+        kernels = {
+            "latent_attn prefill": {"ms": pre_ops["latent_attn"], "tflops": attn_flops / pre_ops["latent_attn"] / 1e9,
+                                    "of_measured_tensor": attn_flops / (pre_ops["latent_attn"] * 1e-3) / tens},
+            "latent_attn decode": {"ms": dec_ops["latent_attn"], "gbs": DB * ctx * D * 2 / dec_ops["latent_attn"] / 1e6,
+                                   "of_measured_hbm": DB * ctx * D * 2 / (dec_ops["latent_attn"] * 1e-3) / hbm},
+            "ssm_scan decode": {"ms": dec_ops["ssm_scan"], "of_measured_hbm":
+                                DB * ss["heads"] * ss["state"] * ss["vdim"] * 8 / (dec_ops["ssm_scan"] * 1e-3) / hbm},
+            "mlstm_scan decode": {"ms": dec_ops["mlstm_scan"], "of_measured_hbm":
+                                  DB * ml["heads"] * ml["dim"] * ml["vdim"] * 8 / (dec_ops["mlstm_scan"] * 1e-3) / hbm},
+            "ssm_scan prefill": {"ms": pre_ops["ssm_scan"], "tokens_per_s": PB * PL / (pre_ops["ssm_scan"] * 1e-3)},
+            "mlstm_scan prefill": {"ms": pre_ops["mlstm_scan"], "tokens_per_s": PB * PL / (pre_ops["mlstm_scan"] * 1e-3)},
+        }
+        from tgis_b200.models.custom_modeling.fetotar_modeling import tensor_shapes
+        shapes = tensor_shapes(raw)
+        lin_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1]
+                    if n.split(".")[-1] in ("in", "o", "q", "k", "v", "g", "i", "f", "dq", "uq", "dkv", "gate", "up", "down", "head")
+                    and not n.startswith("side") and ".side." not in n)
+        lin_flops = 2 * PB * PL * (lin_w - shapes["head"][0] * shapes["head"][1]) + 2 * PB * shapes["head"][0] * shapes["head"][1]
+        kernels["linear prefill (all projections)"] = {"ms": pre_ops["linear"], "of_measured_tensor": lin_flops / (pre_ops["linear"] * 1e-3) / tens}
+        kernels["linear decode (all projections)"] = {"ms": dec_ops["linear"], "of_measured_hbm": lin_w * 2 / (dec_ops["linear"] * 1e-3) / hbm}
+        results.append({"model": f"fetotar-w{width}", "dtype": "bf16", "layers": 3, "prefill_tokens_per_s": PB * PL / (pre_ms * 1e-3),
+                        "decode_tokens_per_s": DB / (dec_ms * 1e-3), "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms,
+                        "prefill_ms_by_op": {k: round(v, 4) for k, v in pre_ops.items()},
+                        "decode_ms_by_op": {k: round(v, 4) for k, v in dec_ops.items()}, "kernels": kernels})
+        del model, engine, weights
+        gc.collect()
+        torch.cuda.empty_cache()
+
+        # ---------------------------------------------------------------- the equal-size GPT-NeoX partner
+        wl = f"neox-w{width}"
+        nmodel, ncfg = build_model(wl, 1, 0, blocks=(DB + PB) * ((DL + 96) // 16 + 2))
+        tok = nmodel.tokenizer
+        names16 = ["gemm_f16", "layernorm_residual", "rope_kv_write_paged", "attn_prefill_varlen", "attn_decode_paged", "gelu", "embedding",
+                   "argmax"]
+
+        def nprefill(B, L, n_new, keep=False):
+            batch, _ = nmodel.batch_type.from_pb(make_batch_pb(B, L, n_new), tok, torch.float16, nmodel.device, None, None, True)
+            nmodel.generate_token(batch, first=True)
+            if keep:
+                return batch
+            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+        with torch.inference_mode():
+            for _ in range(Wm):
+                nprefill(PB, PL, 2)
+            npre_ms = timed(lambda: nprefill(PB, PL, 2), K)
+            log = []
+            saved = _timed_ops(ops_f16, names16, log)
+            nprefill(PB, PL, 2)
+            npre_ops = _by_op(log)
+            for n, fn in saved.items():
+                setattr(ops_f16, n, fn)
+            os.environ["B200_PY_FUSED_STEP"] = "0"  # op by op, as the hybrid model runs: like is compared with like
+            batch = nprefill(DB, DL, Wm + K + 8, keep=True)
+            for _ in range(Wm):
+                nmodel.generate_token(batch)
+            ndec_ms = timed(lambda: nmodel.generate_token(batch), K)
+            log = []
+            saved = _timed_ops(ops_f16, names16, log)
+            nmodel.generate_token(batch)
+            ndec_ops = _by_op(log)
+            for n, fn in saved.items():
+                setattr(ops_f16, n, fn)
+            os.environ.pop("B200_PY_FUSED_STEP", None)
+            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+        hd, nh = 128, width // 128
+        nattn_flops = PB * 4 * (PL * PL // 2) * hd * nh
+        nlin_w = 3 * (4 * width * width + 2 * width * 4 * width) + ncfg.vocab_size * width
+        nkernels = {
+            "attn_prefill_varlen": {"ms": npre_ops.get("attn_prefill_varlen", 0.0),
+                                    "of_measured_tensor": nattn_flops / (max(npre_ops.get("attn_prefill_varlen", 0.0), 1e-9) * 1e-3) / tens},
+            "attn_decode_paged": {"ms": ndec_ops.get("attn_decode_paged", 0.0), "of_measured_hbm":
+                                  3 * DB * ctx * 2 * nh * hd * 2 / (max(ndec_ops.get("attn_decode_paged", 0.0), 1e-9) * 1e-3) / hbm},
+            "gemm_f16 prefill (all projections)": {"ms": npre_ops["gemm_f16"], "of_measured_tensor":
+                                                   (2 * PB * PL * (nlin_w - ncfg.vocab_size * width) + 2 * PB * ncfg.vocab_size * width)
+                                                   / (npre_ops["gemm_f16"] * 1e-3) / tens},
+            "gemm_f16 decode (all projections)": {"ms": ndec_ops["gemm_f16"], "of_measured_hbm": nlin_w * 2 / (ndec_ops["gemm_f16"] * 1e-3) / hbm},
+        }
+        results.append({"model": wl, "dtype": "fp16", "layers": 3, "prefill_tokens_per_s": PB * PL / (npre_ms * 1e-3),
+                        "decode_tokens_per_s": DB / (ndec_ms * 1e-3), "prefill_ms": npre_ms, "decode_ms_per_step": ndec_ms,
+                        "decode_mode": "op by op (B200_PY_FUSED_STEP=0)",
+                        "prefill_ms_by_op": {k: round(v, 4) for k, v in npre_ops.items()},
+                        "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()}, "kernels": nkernels})
+        del nmodel
+        gc.collect()
+        torch.cuda.empty_cache()
+    kernels["latent_attn decode"]["note"] = "3 attention layers in the partner vs 1 latent-attention layer here: compare fractions, not ms"
+    print(json.dumps({"metric": "hybrid_compare", "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": Wm, "data": "synthetic",
+                      "config": {"prefill": [PB, PL], "decode": [DB, DL], "l2": "flushed between timed calls"},
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk.get("source")}, "models": results}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -675,9 +882,13 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=2, help="layers in the CPU baseline's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the second workload, the self-check and the gpt2 CPU line")
+    ap.add_argument("--hybrid-compare", action="store_true",
+                    help="Fetotar beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.hybrid_compare:
+        return run_hybrid_compare(args)
     workload = args.workload or DEFAULT_WORKLOAD
     if workload in MIXED_WORKLOADS:
         if args.impl == "reference":

@@ -180,6 +180,10 @@ int64_t b200_gemm_workspace_bytes_max(int64_t N, int64_t K); /* max over all T: 
  * torch.mm in TensorParallelHead.forward (:257-262). */
 int b200_gemm_f16(const void* x, const void* w, const void* bias, void* y, int64_t T, int64_t N, int64_t K, void* workspace,
                   void* stream);
+/* bfloat16 operands (x [T, K], w [N, K], bias bfloat16 or NULL); y [T, N] bfloat16, or fp32 when out_f32 != 0.  Same kernel
+ * (tcgen05 kind::f16 with bfloat16 operand formats), workspace and rules as b200_gemm_f16. */
+int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* y, int out_f32, int64_t T, int64_t N, int64_t K, void* workspace,
+                   void* stream);
 
 /* one-time conversion of the GPTQ checkpoint tensors of one linear into the kernel's streaming layout ("unit records":
  * one contiguous 8 KB + meta block per (128-feature tile, 128-wide k-block)); replaces

@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200_gemm_workspace_bytes": (_L, [_L, _L, _L]),
     "b200_gemm_workspace_bytes_max": (_L, [_L, _L]),
     "b200_gemm_f16": (_I, [_P, _P, _P, _P, _L, _L, _L, _P, _P]),
+    "b200_gemm_bf16": (_I, [_P, _P, _P, _P, _I, _L, _L, _L, _P, _P]),
     "b200_p2p_handle_bytes": (_I, []),
     "b200_p2p_create": (_I, [_L, _I, _I, ctypes.POINTER(_P), _P]),
     "b200_p2p_connect": (_I, [_P, _P]),
@@ -141,7 +142,8 @@ SEQ_SIGNATURES = {
     "b200_seq_mlstm_scan": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _F, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),
 }
 _SEQ_SHARED = ("b200_last_error", "b200_cuda_peek_error", "b200_launch_count", "b200_kv_alloc_create", "b200_kv_alloc_destroy",
-               "b200_kv_alloc_num_free", "b200_kv_alloc_take", "b200_kv_alloc_release", "b200_decode_advance")
+               "b200_kv_alloc_num_free", "b200_kv_alloc_take", "b200_kv_alloc_release", "b200_decode_advance", "b200_gemm_bf16",
+               "b200_gemm_workspace_bytes_max")
 
 _lib = None
 _seq_lib = None

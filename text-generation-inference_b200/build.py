@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "libb200_tgis.so")
 SEQ_LIB = os.path.join(HERE, "libb200_seq.so")
-SEQ_EXTRA_SOURCES = ("runtime.cu", "kv_alloc.cu")
+SEQ_EXTRA_SOURCES = ("runtime.cu", "kv_alloc.cu", "gemm_f16.cu")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -15,8 +15,24 @@
 #include "../../include/b200_tgis.h"
 
 #include <cstdlib>
+#include <cuda_bf16.h>
 
 namespace b200 {
+
+// Element formats of one instantiation: 0 = fp16 operands, fp16 output (the flash families); 1 = bfloat16 operands, bfloat16
+// output; 2 = bfloat16 operands, fp32 output (hybrid families: projections whose results enter a recurrence, a norm or the
+// soft-max stay in 32 bits).  Same pipeline; the instruction descriptor's operand formats and the epilogue's stores differ.
+template <int FMT>
+__device__ __forceinline__ float gemm_load_bias(const void* bias, int n) {
+  if constexpr (FMT == 0) return __half2float(reinterpret_cast<const __half*>(bias)[n]);
+  else return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
+}
+template <int FMT>
+__device__ __forceinline__ void gemm_store(void* y, size_t i, float v) {
+  if constexpr (FMT == 0) reinterpret_cast<__half*>(y)[i] = __float2half_rn(v);
+  else if constexpr (FMT == 1) reinterpret_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(y)[i] = v;
+}
 
 constexpr int kGemmThreads = 192;
 constexpr int kTileM = 128;  // features per tile
@@ -34,10 +50,10 @@ struct GemmF16Cfg {
 };
 
 struct F16Params {
-  __half* y;
+  void* y;
   float* partial;  // [token tile][feature tile][contributor][TN][128] fp32
   int* counters;   // [token tile][feature tile]
-  const __half* bias;
+  const void* bias;
   int T, N;
   int nkb;            // 64-wide k-blocks per tile
   int n_tiles_n;      // feature tiles
@@ -47,7 +63,7 @@ struct F16Params {
   int defer;          // 1: leave every tile segment as an fp32 partial for the consumer kernel (B200SplitK), no fix-up
 };
 
-template <int TN>
+template <int TN, int FMT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const F16Params p) {
   using C = GemmF16Cfg<TN>;
@@ -116,7 +132,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = umma_idesc_f16_f32acc(kTileM, TN);
+    constexpr uint32_t idesc = umma_idesc_f16_f32acc(kTileM, TN) | (FMT != 0 ? ((1u << 7) | (1u << 10)) : 0u);  // a/b format 1 = bf16
     int seg = 0, kb = kb0;
     for (int i = 0; i < n_units; ++i) {
       const bool seg_first = (i == 0) || kb == 0;
@@ -158,7 +174,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const int tix = blockIdx.y * p.n_tiles_n + tile;
       mbar_wait(tmem_full, seg & 1);
       tcgen05_fence_after();
-      const float bv = (p.bias && n_ok) ? __half2float(p.bias[n]) : 0.f;
+      const float bv = (p.bias && n_ok) ? gemm_load_bias<FMT>(p.bias, n) : 0.f;
       float* part = p.partial + ((size_t)tix * p.max_contrib + my_contrib) * (TN * kTileM);
 #pragma unroll 1
       for (int c = 0; c < TN; c += 16) {
@@ -170,7 +186,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
-              if (t < p.T) p.y[(size_t)t * p.N + n] = __float2half_rn(__uint_as_float(d[j]) + bv);
+              if (t < p.T) gemm_store<FMT>(p.y, (size_t)t * p.N + n, __uint_as_float(d[j]) + bv);
             }
           }
         } else {
@@ -230,21 +246,21 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               const int nn = tile * kTileM + mm;
               if (idx < n_vec) {
                 const float a4[4] = {acc[e].x, acc[e].y, acc[e].z, acc[e].w};
-                if (vec_ok && nn + 3 < p.N) {
+                if (FMT == 0 && vec_ok && nn + 3 < p.N) {
                   float b4[4] = {0.f, 0.f, 0.f, 0.f};
                   if (p.bias) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) b4[q] = __half2float(p.bias[nn + q]);
+                    for (int q = 0; q < 4; ++q) b4[q] = gemm_load_bias<FMT>(p.bias, nn + q);
                   }
                   uint2 o;
                   o.x = pack_half2(a4[0] + b4[0], a4[1] + b4[1]);
                   o.y = pack_half2(a4[2] + b4[2], a4[3] + b4[3]);
-                  *reinterpret_cast<uint2*>(&p.y[(size_t)(t0 + tt) * p.N + nn]) = o;
+                  *reinterpret_cast<uint2*>(&reinterpret_cast<__half*>(p.y)[(size_t)(t0 + tt) * p.N + nn]) = o;
                 } else {
 #pragma unroll
                   for (int q = 0; q < 4; ++q)
                     if (nn + q < p.N)
-                      p.y[(size_t)(t0 + tt) * p.N + nn + q] = __float2half_rn(a4[q] + (p.bias ? __half2float(p.bias[nn + q]) : 0.f));
+                      gemm_store<FMT>(p.y, (size_t)(t0 + tt) * p.N + nn + q, a4[q] + (p.bias ? gemm_load_bias<FMT>(p.bias, nn + q) : 0.f));
                 }
               }
             }
@@ -309,8 +325,9 @@ static F16Plan plan_f16(int64_t T, int64_t N, int64_t K, int sms, bool defer = f
 
 using namespace b200;
 
-int64_t b200_w4_partial_bytes(int64_t T, int64_t N, int64_t K);  // gemm_w4a16.cu (stream-K partials)
-void b200_w4_plan_debug(int64_t T, int64_t N, int64_t K, int sms, int32_t* out);
+// gemm_w4a16.cu; weak: a library built without the int4 kernels (libb200_seq.so) resolves them to null
+__attribute__((weak)) int64_t b200_w4_partial_bytes(int64_t T, int64_t N, int64_t K);  // stream-K partials
+__attribute__((weak)) void b200_w4_plan_debug(int64_t T, int64_t N, int64_t K, int sms, int32_t* out);
 
 // tests (no GPU needed): the stream-K plan of one GEMM launch.  kind 0 = fp16 weights, 1 = int4.
 // out[8] = {token tile, k-blocks per tile, feature tiles (int4: super-tiles), token tiles, units per CTA, CTAs,
@@ -321,6 +338,7 @@ extern "C" int b200_debug_gemm_plan(int kind, int64_t T, int64_t N, int64_t K, i
     return B200_ERR_ARG;
   }
   if (kind == 1) {
+    if (!b200_w4_plan_debug) { b200_set_last_error("debug_gemm_plan: this library has no int4 kernels"); return B200_ERR_UNSUPPORTED; }
     b200_w4_plan_debug(T, N, K, sms, out);
     return B200_OK;
   }
@@ -338,7 +356,7 @@ extern "C" int64_t b200_gemm_workspace_bytes(int64_t T, int64_t N, int64_t K) {
     const int64_t fd = (int64_t)pd.n_tiles_n * pd.max_contrib * pd.TN * kTileM * 4;
     if (fd > f16) f16 = fd;
   }
-  const int64_t w4 = b200_w4_partial_bytes(T, N, K);
+  const int64_t w4 = b200_w4_partial_bytes ? b200_w4_partial_bytes(T, N, K) : 0;
   return kCounterBytes + (f16 > w4 ? f16 : w4);
 }
 
@@ -352,21 +370,21 @@ extern "C" int64_t b200_gemm_workspace_bytes_max(int64_t N, int64_t K) {
   return best;
 }
 
-template <int TN>
+template <int TN, int FMT>
 static int launch_gemm_f16(const CUtensorMap* mw, const CUtensorMap* mx, void* y, void* workspace, const void* bias, int T, int N,
                            const F16Plan& pl, int defer, cudaStream_t st) {
   using C = GemmF16Cfg<TN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel<TN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) { b200_set_last_error(cudaGetErrorString(e)); return B200_ERR_CUDA; }
     configured = true;
   }
   F16Params p;
-  p.y = (__half*)y;
+  p.y = y;
   p.counters = (int*)workspace;
   p.partial = workspace ? (float*)((char*)workspace + kCounterBytes) : nullptr;
-  p.bias = (const __half*)bias;
+  p.bias = bias;
   p.T = T;
   p.N = N;
   p.nkb = pl.nkb;
@@ -377,7 +395,7 @@ static int launch_gemm_f16(const CUtensorMap* mw, const CUtensorMap* mx, void* y
   p.defer = defer;
   dim3 grid(pl.n_ctas, pl.n_tiles_t, 1);
   b200_timing_mark(B200_TIME_GEMM_F16, 0, st);
-  B200_LAUNCH(gemm_f16_kernel<TN>, grid, dim3(kGemmThreads), (size_t)C::kSmemBytes, st, *mw, *mx, p);
+  B200_LAUNCH((gemm_f16_kernel<TN, FMT>), grid, dim3(kGemmThreads), (size_t)C::kSmemBytes, st, *mw, *mx, p);
   b200_timing_mark(B200_TIME_GEMM_F16, 1, st);
   b200_count_launches(1);
   return B200_OK;
@@ -386,6 +404,7 @@ static int launch_gemm_f16(const CUtensorMap* mw, const CUtensorMap* mx, void* y
 // workspace: >= b200_gemm_workspace_bytes(T, N, K) bytes whose first 64 KiB (tile counters) were zeroed once by the
 // caller, or NULL (every CTA then takes whole tiles: no stream-K).
 // splitk != NULL: deferred reduction (see b200_gemm_w4a16_deferred): y is not written.
+template <int FMT>
 static int gemm_f16_impl(const void* x, const void* w, const void* bias, void* y, int64_t T, int64_t N, int64_t K, void* workspace,
                          B200SplitK* splitk, void* stream) {
   if (T == 0 || N == 0) return B200_OK;
@@ -419,19 +438,26 @@ static int gemm_f16_impl(const void* x, const void* w, const void* bias, void* y
   cudaStream_t st = (cudaStream_t)stream;
   const int df = defer ? 1 : 0;
   switch (pl.TN) {
-    case 16: return launch_gemm_f16<16>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
-    case 32: return launch_gemm_f16<32>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
-    case 64: return launch_gemm_f16<64>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
-    case 128: return launch_gemm_f16<128>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
-    default: return launch_gemm_f16<256>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
+    case 16: return launch_gemm_f16<16, FMT>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
+    case 32: return launch_gemm_f16<32, FMT>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
+    case 64: return launch_gemm_f16<64, FMT>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
+    case 128: return launch_gemm_f16<128, FMT>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
+    default: return launch_gemm_f16<256, FMT>(mw, mx, y, workspace, bias, (int)T, (int)N, pl, df, st);
   }
 }
 extern "C" int b200_gemm_f16(const void* x, const void* w, const void* bias, void* y, int64_t T, int64_t N, int64_t K,
                              void* workspace, void* stream) {
-  return gemm_f16_impl(x, w, bias, y, T, N, K, workspace, nullptr, stream);
+  return gemm_f16_impl<0>(x, w, bias, y, T, N, K, workspace, nullptr, stream);
+}
+// bfloat16 x [T, K] and w [N, K] (bias bfloat16 or NULL) -> y [T, N] bfloat16, or fp32 when out_f32 != 0.  Same kernel,
+// workspace and rules as b200_gemm_f16.
+extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* y, int out_f32, int64_t T, int64_t N, int64_t K,
+                              void* workspace, void* stream) {
+  if (out_f32) return gemm_f16_impl<2>(x, w, bias, y, T, N, K, workspace, nullptr, stream);
+  return gemm_f16_impl<1>(x, w, bias, y, T, N, K, workspace, nullptr, stream);
 }
 extern "C" int b200_gemm_f16_deferred(const void* x, const void* w, const void* bias, int64_t T, int64_t N, int64_t K, void* workspace,
                                       B200SplitK* splitk, void* stream) {
   if (!splitk) { b200_set_last_error("gemm_f16_deferred: splitk is NULL"); return B200_ERR_ARG; }
-  return gemm_f16_impl(x, w, bias, nullptr, T, N, K, workspace, splitk, stream);
+  return gemm_f16_impl<0>(x, w, bias, nullptr, T, N, K, workspace, splitk, stream);
 }

@@ -64,6 +64,37 @@ class FetotarConfig:
             return cls(json.load(f))
 
 
+def tensor_shapes(raw: Dict[str, Any]) -> Dict[str, tuple]:
+    """name -> shape of every checkpoint tensor of a configuration (synthetic checkpoints, load-time validation)"""
+    W, V, side = int(raw["width"]), int(raw["vocab"]), int(raw["token_side"]["dim"])
+    out = {"embed": (V, W), "side.embed": (V, side * len(raw["layers"])), "final.norm": (W,), "final.norm.b": (W,), "head": (V, W)}
+    for i, layer in enumerate(raw["layers"]):
+        m, mix = layer["mixer"], {}
+        if layer["type"] == "mlstm":
+            qk, vg = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            mix = {"q": (qk, W), "k": (qk, W), "v": (vg, W), "g": (vg, W), "i": (m["heads"], W), "i.b": (m["heads"],), "f": (m["heads"], W),
+                   "f.b": (m["heads"],), "norm": (vg,), "o": (W, vg)}
+        elif layer["type"] == "mamba2":
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            mix = {"in": (2 * inner + 2 * gn + m["heads"], W), "conv": (inner + 2 * gn, m["conv"]), "conv.b": (inner + 2 * gn,),
+                   "dt_bias": (m["heads"],), "A_log": (m["heads"],), "D": (m["heads"],), "norm": (inner,), "o": (W, inner)}
+        elif layer["type"] == "latent_attention":
+            H = m["heads"]
+            mix = {"dq": (m["q_rank"], W), "dq.norm": (m["q_rank"],), "uq": (H * (m["dim"] + m["rot_dim"]), m["q_rank"]),
+                   "dkv": (m["kv_rank"] + m["rot_dim"], W), "dkv.norm": (m["kv_rank"],), "uk": (H * m["dim"], m["kv_rank"]),
+                   "uv": (H * m["vdim"], m["kv_rank"]), "g": (H * m["vdim"], W), "o": (W, H * m["vdim"])}
+        names = ["norm1", "norm1b"] + (["norm2", "norm2b"] if layer.get("mlp") else [])
+        for n in names:
+            out[f"l{i}.{n}"] = (W,)
+            out[f"l{i}.{n}.b"] = (W,)
+        out.update({f"l{i}.mix.{k}": v for k, v in mix.items()})
+        if layer.get("mlp"):
+            ff = int(layer["mlp"]["ff"])
+            out.update({f"l{i}.mlp.gate": (ff, W), f"l{i}.mlp.up": (ff, W), f"l{i}.mlp.down": (W, ff)})
+        out.update({f"l{i}.side.gate": (side, W), f"l{i}.side.proj": (W, side), f"l{i}.side.norm": (W,)})
+    return out
+
+
 def build_mixer(kind: str, prefix: str, m: Dict[str, Any], weights, eps: float) -> nn.Module:
     if kind == "mlstm":
         return MLSTMMixer(prefix, weights, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), gate_cap=float(m["gate_cap"]), eps=eps)

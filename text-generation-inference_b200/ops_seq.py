@@ -6,6 +6,7 @@ soft-max, recurrences, states and the residual stream are fp32 in both.  CUDA te
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -51,9 +52,25 @@ class RaggedStep:
     state_slots: Optional[torch.Tensor]  # [B] int32
 
 
+_TC_GEMM = os.getenv("B200_SEQ_TC_GEMM", "1") != "0"
+_gemm_ws = {}
+
+
+def _gemm_workspace(device, N: int, K: int) -> torch.Tensor:
+    """per-device split-K workspace of the tensor-core product (tile counters zeroed once; the kernel re-arms them)"""
+    need = _lib.load_seq().b200_gemm_workspace_bytes_max(N, K)
+    ws = _gemm_ws.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _gemm_ws[device] = ws
+    return ws
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x [M, K] (any row stride) @ w [N, K]^T -> [M, N]; fp32 accumulation in ascending k."""
+    """x [M, K] @ w [N, K]^T -> [M, N], fp32 accumulation.  bfloat16 operands go to the tcgen05 product (csrc/gemm_f16.cu,
+    output bfloat16 or fp32) when they are dense and K is a multiple of 8 of at least 64; everything else - float32 operands
+    (a true 32-bit product), row-strided slices, small or odd K - to the plain product with ascending-k accumulation."""
     _cuda(x, w, bias)
     assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
     M, K = x.shape
@@ -61,6 +78,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
     assert out.stride(1) == 1
+    if (_TC_GEMM and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and K >= 64 and x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+            and (bias is None or bias.dtype == torch.bfloat16) and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and M > 0):
+        ws = _gemm_workspace(x.device, N, K)
+        _lib.check_seq(_lib.load_seq().b200_gemm_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), int(out.dtype == torch.float32), M, N, K,
+                                                      _ptr(ws), _stream()), "gemm_bf16")
+        return out
     _lib.check_seq(_lib.load_seq().b200_seq_linear(_ptr(x), _dt(x), x.stride(0), 0, _ptr(w), _dt(w), w.stride(0), 0, _ptr(bias), _ptr(out),
                                                    _dt(out), out.stride(0), 0, M, N, K, 1, _stream()), "seq_linear")
     return out

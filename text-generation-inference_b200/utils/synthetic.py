@@ -25,7 +25,52 @@ NEOX_ARCHS = {
     # name: (hidden, intermediate, layers, heads, vocab, rotary_pct)
     "pythia-12b": (5120, 20480, 36, 40, 50688, 0.25),  # head size 128 (gpt-neox-20b's 96 is not a kernel instantiation)
     "tiny-neox": (256, 1024, 2, 4, 512, 0.25),
+    # three layers of a real model's widths: the equal-size partners of the hybrid configurations below
+    "neox-w2048": (2048, 8192, 3, 16, 32000, 0.25),
+    "neox-w4096": (4096, 16384, 3, 32, 32000, 0.25),
 }
+
+
+def fetotar_config(name: str) -> dict:
+    """Three layers (one of each mixer) at the widths of the `neox-w*` partners: raw config.json of the Fetotar family."""
+    W = {"fetotar-w2048": 2048, "fetotar-w4096": 4096}[name]
+    heads = W // 128
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "fast": 32.0, "original": 4096, "slow": 1.0}}
+    layers = [
+        {"type": "mlstm", "mixer": {"dim": 128, "gate_cap": 15.0, "heads": heads // 2, "vdim": 256}, "mlp": None},
+        {"type": "latent_attention", "mixer": {"dim": 128, "heads": heads, "kv_rank": 512, "mask": {"size": 4096}, "q_rank": 1536, "rot": rot,
+                                               "rot_dim": 64, "scale": 192 ** -0.5, "vdim": 128},
+         "mlp": {"ff": W * 11 // 4, "kind": "dense", "limit": 7.0}},
+        {"type": "mamba2", "mixer": {"conv": 4, "groups": 8, "heads": 2 * W // 64, "norm_groups": 8, "state": 128, "vdim": 64}, "mlp": None},
+    ]
+    return {"architecture": "Fetotar", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-5}, "token_side": {"dim": 256},
+            "vocab": 32000, "width": W}
+
+
+class SyntheticHybridWeights:
+    """Seeded random tensors of a Fetotar configuration, generated on the device by name (the `get_tensor` side of `Weights`)."""
+
+    def __init__(self, raw_config: dict, device, dtype, process_group, seed: int = 1234):
+        from ..models.custom_modeling.fetotar_modeling import tensor_shapes
+        self.shapes, self.device, self.dtype, self.process_group, self.seed = tensor_shapes(raw_config), device, dtype, process_group, seed
+
+    def get_tensor(self, name: str) -> torch.Tensor:
+        shape = self.shapes[name]
+        gen = torch.Generator(device=self.device).manual_seed(self.seed * 1000003 + zlib.crc32(name.encode()))
+        leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
+        if len(shape) == 2:
+            std = 0.5 if leaf.endswith("conv") else 1.0 / (shape[1] ** 0.5)
+            t = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, std, generator=gen)
+        elif leaf in ("mix.A_log", "mix.dt_bias"):
+            t = torch.rand(shape, generator=gen, device=self.device) * 2.0 - 2.0
+        elif leaf == "mix.f.b":
+            t = torch.full(shape, 3.0, device=self.device)
+        elif leaf.endswith(".b"):
+            t = torch.zeros(shape, device=self.device)
+        else:
+            t = torch.ones(shape, device=self.device)
+        return t.to(self.dtype)
+
 
 
 def llama_config(name: str, quantize: Optional[str] = None, max_position_embeddings: int = 4096, num_layers: Optional[int] = None):
