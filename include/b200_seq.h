@@ -28,7 +28,8 @@ int b200_seq_linear(const void* A, int a_dt, int64_t lda, int64_t strideA, const
 /* out[t] = table[ids[t]] * scale, fp32 */
 int b200_seq_embed_scale(const void* table, int dt, const int64_t* ids, float scale, float* out, int64_t T, int64_t W, int64_t V,
                          void* stream);
-/* LayerNorm with weight and bias of rows of type x_dt; resid == NULL: out (type dt) = LN(x), else resid (fp32) += LN(x) */
+/* LayerNorm with weight and bias of rows of type x_dt; resid == NULL: out (type dt) = LN(x), else resid (fp32) += LN(x) and out,
+ * when given, receives the updated residual rows in type dt */
 int b200_seq_layernorm(const void* x, int x_dt, const void* w, const void* b, int dt, void* out, float* resid, int64_t T, int64_t W,
                        float eps, void* stream);
 /* per group of n columns: v / sqrt(mean v^2 + eps) * w; gate_kind 0 none, 1 SiLU(gate) before the statistics, 2 sigmoid(gate)
@@ -37,9 +38,10 @@ int b200_seq_group_rmsnorm_gate(const float* x, int64_t ldx, const float* gate, 
                                 int groups, int n, float eps, void* out, int out_dt, int64_t ldo, int64_t T, void* stream);
 /* [g | u] rows -> min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) + 1) */
 int b200_seq_ff_clamped_gate(const void* gu, void* out, int dt, int64_t rows, int64_t F, float limit, float alpha, void* stream);
-/* resid += unit_rms(Wp (gelu_tanh(Wg resid) * table[id, col0 : col0 + dim])) * nw */
-int b200_seq_token_side(float* resid, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V,
-                        const void* Wg, const void* Wp, const void* nw, int dt, int64_t T, int64_t W, float eps, void* stream);
+/* per-layer token input, around its two projections: out = gelu_tanh(a) * table[id, col0 : col0 + dim]; resid += unit_rms(y) * w */
+int b200_seq_side_gate(const float* a, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V, void* out,
+                       int dt, int64_t rows, void* stream);
+int b200_seq_rms_add(const float* y, const void* w, int dt, float* resid, int64_t T, int64_t W, float eps, void* stream);
 /* cache row of every token = [unit_rms(latent) * w | rotated key part]; q_abs[:, :, R:] = rotated query parts */
 int b200_seq_latent_prepare(const float* down, int64_t ld_down, int col_c, int col_kr, const float* q, int64_t ld_q, int q_head_stride,
                             int q_rot_off, const void* cnorm_w, const float* cos_t, const float* sin_t, const int64_t* position_ids,

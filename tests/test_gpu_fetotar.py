@@ -61,7 +61,7 @@ def _run_cut(model, tokens, cuts):
     return torch.cat(rows)
 
 
-TOL32, TOL16 = 2e-4, 0.12
+TOL32, TOL16 = 2e-4, 0.3
 
 
 class _DictWeights:
@@ -124,8 +124,12 @@ def test_row_kernels_match_reference():
     p = {"gate": torch.randn(dim, W, generator=g) * 0.3, "proj": torch.randn(W, dim, generator=g), "norm": torch.randn(W, generator=g)}
     ref = orc.token_side(x.double(), ids, 1, table.double(), {k: v.double() for k, v in p.items()}, dim, 1e-5)
     acc = x.clone().to(DEV)
-    ops.token_side(acc, ids.to(DEV), table.to(DEV), dim, dim, p["gate"].to(DEV), p["proj"].to(DEV), p["norm"].to(DEV), 1e-5)
+    ops.token_side(acc, acc, ids.to(DEV), table.to(DEV), dim, dim, p["gate"].to(DEV), p["proj"].to(DEV), p["norm"].to(DEV), 1e-5)
     assert torch.allclose(acc.cpu().double(), ref, atol=1e-4)
+    # the residual update that also hands out the typed copy for the next projection
+    acc, xb = res.clone().to(DEV), x.to(DEV).bfloat16()
+    copy = ops.layernorm_into_residual(xb, w.to(DEV).bfloat16(), b.to(DEV).bfloat16(), 1e-5, acc, typed_copy=True)
+    assert copy.dtype == torch.bfloat16 and torch.equal(copy, acc.bfloat16())
     emb = ops.embed_scale(table.to(DEV), ids.to(DEV), 2.5)
     assert torch.equal(emb.cpu(), table[ids] * 2.5)
     # the product kernel in every type combination the mixers use, odd sizes, bias, per-head strides
@@ -161,6 +165,8 @@ MIXER_CASES = [
     ("mamba2", {"conv": 4, "groups": 3, "heads": 3, "norm_groups": 1, "state": 16, "vdim": 8}),
     ("latent_attention", {"dim": 10, "heads": 3, "kv_rank": 14, "mask": {"size": 9}, "q_rank": 18, "rot_dim": 6, "scale": 0.4, "vdim": 12,
                           "rot": {"base": 5000.0, "dims": 6, "scaling": {"factor": 3.0, "fast": 24.0, "original": 64, "slow": 2.0}}}),
+    ("latent_attention", {"dim": 24, "heads": 20, "kv_rank": 64, "mask": {"size": 70}, "q_rank": 16, "rot_dim": 16, "scale": 0.2, "vdim": 8,
+                          "rot": {"base": 300.0, "dims": 16}}),
     ("latent_attention", {"dim": 8, "heads": 9, "kv_rank": 40, "mask": {"size": 33}, "q_rank": 12, "rot_dim": 8, "scale": 0.3, "vdim": 4,
                           "rot": {"base": 100.0, "dims": 4}}),
 ]
@@ -227,13 +233,14 @@ def _attn_reference(q_abs, rows, pos_of_row, seq_of_row, q_pos, q_seq, R, window
     return out
 
 
+@pytest.mark.parametrize("R,r", [(40, 8), (64, 16)])  # the second shape takes the tensor-core kernel when the cache is bfloat16
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_latent_attention_window_edges_page_borders_and_far_keys(dtype):
+def test_latent_attention_window_edges_page_borders_and_far_keys(dtype, R, r):
     """one key per query is made to dominate the soft-max; it sits just inside or just outside the window, on either side of a
     page border, at the first positions, or hundreds of tokens back - for query rows inside a prompt and for single decoded tokens"""
     import tgis_b200  # noqa: F401
     from tgis_b200 import ops_seq as ops
-    R, r, H, window, scale = 40, 8, 3, 48, 1.0
+    H, window, scale = 3, 48, 1.0
     D = R + r
     g = torch.Generator().manual_seed(3)
     L = 420
@@ -257,14 +264,14 @@ def test_latent_attention_window_edges_page_borders_and_far_keys(dtype):
             st = _step([(p, 1)], 32)
             st.block_table = full.block_table
             got = ops.latent_attn(q_abs[i:i + 1].to(DEV).contiguous(), cache, st, R, r, win, scale).cpu().double()
-            assert torch.allclose(got, ref[i:i + 1], atol=1e-4 if dtype == torch.float32 else 2e-2), (far, pairs[i])
+            assert torch.allclose(got, ref[i:i + 1], atol=1e-4 if dtype == torch.float32 else 3e-2), (far, pairs[i])
         # and all positions of the sequence as one prompt: row p is query p
         qs = torch.randn(L, H, D, generator=g) * 0.2
         for i, (p, j) in enumerate(pairs):
             qs[p] = q_abs[i]
         got = ops.latent_attn(qs.to(DEV).contiguous(), cache, full, R, r, win, scale).cpu().double()
         for p, i in {p: i for i, p in enumerate(q_pos)}.items():  # a position listed twice carries its last query
-            assert torch.allclose(got[p], ref[i], atol=1e-4 if dtype == torch.float32 else 2e-2), (far, "prompt", pairs[i])
+            assert torch.allclose(got[p], ref[i], atol=1e-4 if dtype == torch.float32 else 3e-2), (far, "prompt", pairs[i])
 
 
 # ------------------------------------------------------------------------------------------------ the model through the engine

@@ -16,6 +16,8 @@
 // by the host with any frequency scaling and amplitude factor folded in); elements past rot_dims pass unchanged.
 #include "seq_common.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 namespace seq {
 
@@ -147,6 +149,178 @@ __global__ void __launch_bounds__(kHeadsPerBlock * 32) latent_attn_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form for bfloat16 caches.  One block per (query token, 16 heads): the 16 heads are the M rows of m16n8k16 MMAs, so
+// one pass over the token's window serves them all - the cache row of a key is the B operand of S = Q K^T (all D columns) and,
+// read transposed, of O += P V (its first R columns).  Key tiles of 64 rows come in with 16-byte cp.async; each of the four warps
+// scores 16 keys of the tile, the row maxima and sums meet in shared memory (fp32 online soft-max, every warp keeps the same
+// running max and sum), P goes to shared memory as bfloat16, and each warp accumulates a quarter of the R output columns in
+// registers.  Needs D % 16 == 0, R % 64 == 0, R <= 512; other shapes and float32 caches take latent_attn_kernel above.
+// ------------------------------------------------------------------------------------------------------------------------
+constexpr int kMmaKeys = 64, kMmaThreads = 128, kMmaPad = 8;
+
+template <int NTW>  // n-tiles (8 output columns each) per warp: R = 32 * NTW
+__global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
+    const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table, int64_t bt_stride,
+    const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H, int R, int D, int window,
+    float scale, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int DP = D + kMmaPad;                // padded row (elements): rows 16 bytes apart modulo 128 -> conflict-free ldmatrix
+  constexpr int PP = kMmaKeys + kMmaPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][DP]
+  __nv_bfloat16* Ks = Qs + 16 * DP;                                  // [64][DP]
+  __nv_bfloat16* Ps = Ks + kMmaKeys * DP;                            // [16][PP]
+  float* red_max = reinterpret_cast<float*>(Ps + 16 * PP);           // [4][16]
+  float* red_sum = red_max + 64;                                     // [4][16]
+  const int64_t t = blockIdx.x;
+  const int h0 = blockIdx.y * 16;
+  const int w = warp_id(), lane = lane_id();
+  const int b = seq_of_token[t];
+  const int p = (int)position_ids[t];
+  const int j_lo = max(0, p - window + 1);
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  for (int idx = threadIdx.x; idx < 16 * D; idx += kMmaThreads) {
+    const int row = idx / D, d = idx % D;
+    const float v = (h0 + row < H) ? q_abs[(t * H + h0 + row) * D + d] * scale : 0.f;
+    Qs[row * DP + d] = __float2bfloat16_rn(v);
+  }
+  const int r0 = lane >> 2, cq = (lane & 3) * 2;   // accumulator rows r0, r0 + 8; columns cq, cq + 1 of an 8-wide tile
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[NTW][4];
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int chunks = D / 8;  // 16-byte pieces of a cache row
+  const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), ps_addr = smem_u32(Ps);
+  for (int j0 = j_lo; j0 <= p; j0 += kMmaKeys) {
+    __syncthreads();  // everyone is done with the previous tile (and Qs is written, first time round)
+    for (int idx = threadIdx.x; idx < kMmaKeys * chunks; idx += kMmaThreads) {
+      const int row = idx / chunks, ch = idx % chunks;
+      const int j = j0 + row;
+      __nv_bfloat16* dst = Ks + row * DP + ch * 8;
+      if (j <= p) {
+        const int64_t crow = (int64_t)table[j / page] * page + j % page;
+        cp_async_16(dst, cache + crow * D + ch * 8, true);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);  // finite: these rows meet p = 0
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    // ---- S = Q K^T for this warp's 16 keys
+    float s[2][4] = {};
+    {
+      const int m = lane >> 3, rr = lane & 7;
+      const uint32_t a_lane = qs_addr + (uint32_t)((((m & 1) * 8 + rr) * DP + (m >> 1) * 8) * 2);
+      const uint32_t b_lane = ks_addr + (uint32_t)(((w * 16 + (m >> 1) * 8 + rr) * DP + (m & 1) * 8) * 2);
+      for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4], bb[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
+        ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + kk * 2);
+        mma_m16n8k16_bf16f32(s[0], a, bb[0], bb[1]);
+        mma_m16n8k16_bf16f32(s[1], a, bb[2], bb[3]);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + w * 16 + nt * 8 + cq + (e & 1);
+        if (j > p) s[nt][e] = -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    }
+    if ((lane & 3) == 0) {
+      red_max[w * 16 + r0] = mx[0];
+      red_max[w * 16 + r0 + 8] = mx[1];
+    }
+    __syncthreads();
+    float m_new[2], corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = r0 + i * 8;
+      const float tm = fmaxf(fmaxf(red_max[row], red_max[16 + row]), fmaxf(red_max[32 + row], red_max[48 + row]));
+      m_new[i] = fmaxf(m_run[i], tm);  // finite: key j0 is visible to every row
+      corr[i] = expf(m_run[i] - m_new[i]);
+      m_run[i] = m_new[i];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = expf(s[nt][0] - m_new[0]), p1 = expf(s[nt][1] - m_new[0]);
+      const float p2 = expf(s[nt][2] - m_new[1]), p3 = expf(s[nt][3] - m_new[1]);
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+      // the sums use the rounded probabilities: numerator and denominator see the same weights
+      sum[0] += __low2float(lo) + __high2float(lo);
+      sum[1] += __low2float(hi) + __high2float(hi);
+      const int col = w * 16 + nt * 8 + cq;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * PP + col) = lo;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * PP + col) = hi;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+    }
+    if ((lane & 3) == 0) {
+      red_sum[w * 16 + r0] = sum[0];
+      red_sum[w * 16 + r0 + 8] = sum[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = r0 + i * 8;
+      l_run[i] = l_run[i] * corr[i] + ((red_sum[row] + red_sum[16 + row]) + (red_sum[32 + row] + red_sum[48 + row]));
+    }
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // ---- O += P V over this warp's NTW * 8 output columns
+    {
+      const int m = lane >> 3, rr = lane & 7;
+      const uint32_t a_lane = ps_addr + (uint32_t)((((m & 1) * 8 + rr) * PP + (m >> 1) * 8) * 2);
+      const uint32_t v_lane = ks_addr + (uint32_t)((((m & 1) * 8 + rr) * DP + w * NTW * 8 + (m >> 1) * 8) * 2);
+#pragma unroll
+      for (int ks = 0; ks < kMmaKeys / 16; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + ks * 32);
+#pragma unroll
+        for (int nt = 0; nt < NTW; nt += 2) {
+          uint32_t bb[4];
+          ldmatrix_x4_trans(bb[0], bb[1], bb[2], bb[3], v_lane + (uint32_t)((ks * 16 * DP + nt * 8) * 2));
+          mma_m16n8k16_bf16f32(o[nt], a, bb[0], bb[1]);
+          mma_m16n8k16_bf16f32(o[nt + 1], a, bb[2], bb[3]);
+        }
+      }
+    }
+  }
+  const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
+#pragma unroll
+  for (int nt = 0; nt < NTW; ++nt) {
+    const int col = (w * NTW + nt) * 8 + cq;
+    if (h0 + r0 < H) {
+      float* dst = out + (t * H + h0 + r0) * R + col;
+      dst[0] = o[nt][0] * inv0;
+      dst[1] = o[nt][1] * inv0;
+    }
+    if (h0 + r0 + 8 < H) {
+      float* dst = out + (t * H + h0 + r0 + 8) * R + col;
+      dst[0] = o[nt][2] * inv1;
+      dst[1] = o[nt][3] * inv1;
+    }
+  }
+}
+
 }  // namespace seq
 }  // namespace b200
 
@@ -189,6 +363,33 @@ extern "C" int b200_seq_latent_attn(const float* q_abs, const void* cache, int d
   if (window <= 0) window = 0x3fffffff;
   const int nr = (R + 31) / 32;
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_ATTN_MMA"); return !(e && e[0] == '0'); }();
+  if (use_mma && dt == B200_DT_BF16 && D % 16 == 0 && R % 64 == 0 && R <= 512 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+    const int ntw = R / 32;
+    const size_t smem = ((size_t)(16 + kMmaKeys) * (D + kMmaPad) + 16 * (kMmaKeys + kMmaPad)) * 2 + 128 * 4;
+    dim3 grid((unsigned)Tq, (unsigned)((H + 15) / 16));
+#define LAM(N)                                                                                                                        \
+  do {                                                                                                                                \
+    static bool cfg = false;                                                                                                          \
+    if (!cfg) { cudaFuncSetAttribute(latent_attn_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
+    B200_LAUNCH((latent_attn_mma_kernel<N>), grid, dim3(kMmaThreads), smem, st, q_abs, (const __nv_bfloat16*)cache, block_table, bt_stride, \
+                seq_of_token, position_ids, out, H, R, D, window, scale, page);                                                       \
+    b200_count_launches(1);                                                                                                           \
+    return B200_OK;                                                                                                                   \
+  } while (0)
+    switch (ntw) {
+      case 2: LAM(2);
+      case 4: LAM(4);
+      case 6: LAM(6);
+      case 8: LAM(8);
+      case 10: LAM(10);
+      case 12: LAM(12);
+      case 14: LAM(14);
+      case 16: LAM(16);
+      default: break;
+    }
+#undef LAM
+  }
 #define LA(NR)                                                                                                                         \
   B200_SEQ_DISPATCH(dt, E, return (launch_latent_attn<E, NR>(q_abs, cache, block_table, bt_stride, seq_of_token, position_ids, out, Tq, H, R, D, \
                                                             window, scale, page, st)))

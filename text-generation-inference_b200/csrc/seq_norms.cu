@@ -21,6 +21,7 @@ __global__ void __launch_bounds__(kRowThreads) embed_scale_kernel(const T* __res
 }
 
 // mode 0: out[t] = LN(x[t]) * w + b  (x fp32 or T, out T)      mode 1: resid[t] += LN(x[t]) * w + b  (resid fp32)
+// In mode 1 `out`, when given, also receives the updated residual row in the activation type (the next projection's input).
 template <typename TX, typename TP, typename TO>
 __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const TX* __restrict__ x, const TP* __restrict__ w, const TP* __restrict__ b,
                                                                 TO* __restrict__ out, float* __restrict__ resid, int W, float eps) {
@@ -44,8 +45,13 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const TX* __rest
   const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
   for (int i = threadIdx.x; i < W; i += kRowThreads) {
     const float y = (row[i] - mean) * rstd * ldf(w + i) + ldf(b + i);
-    if (resid) resid[t * W + i] += y;
-    else stf(out + t * W + i, y);
+    if (resid) {
+      const float r = resid[t * W + i] + y;
+      resid[t * W + i] = r;
+      if (out) stf(out + t * W + i, r);
+    } else {
+      stf(out + t * W + i, y);
+    }
   }
 }
 
@@ -98,42 +104,36 @@ __global__ void ff_clamped_gate_kernel(const T* __restrict__ gu, T* __restrict__
   }
 }
 
-// Per-layer token input added to the stream: e = side_table[id, col0 : col0 + dim]; g = gelu_tanh(Wg x) * e; y = Wp g;
-// x += y / sqrt(mean(y^2) + eps) * nw.   Wg [dim, W], Wp [W, dim].  dim is small (tens): one block does the row.
+// Per-layer token input, the two row kernels around its projections:  g = gelu_tanh(a) * table[id, col0 : col0 + dim]  (a = Wg x),
+// and  resid += y / sqrt(mean(y^2) + eps) * w  (y = Wp g).
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads) token_side_kernel(float* __restrict__ resid, const int64_t* __restrict__ ids, const T* __restrict__ table,
-                                                                 int64_t ld_table, int64_t col0, int dim, int64_t V, const T* __restrict__ Wg,
-                                                                 const T* __restrict__ Wp, const T* __restrict__ nw, int W, float eps) {
+__global__ void side_gate_kernel(const float* __restrict__ a, const int64_t* __restrict__ ids, const T* __restrict__ table, int64_t ld_table,
+                                 int64_t col0, int dim, int64_t V, T* __restrict__ out, int64_t rows) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
-  float* xs = sm;       // [W]
-  float* gs = sm + W;   // [dim]
+  const int64_t total = rows * dim;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / dim, j = i % dim;
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    stf(out + i, gelu_tanh_f(a[i]) * ldf(table + id * ld_table + col0 + j));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) rms_add_kernel(const float* __restrict__ y, const T* __restrict__ w, float* __restrict__ resid, int W,
+                                                              float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
-  int64_t id = ids[t];
-  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-  for (int i = threadIdx.x; i < W; i += kRowThreads) xs[i] = resid[t * W + i];
-  __syncthreads();
-  for (int j = warp_id(); j < dim; j += kRowThreads / 32) {
-    float a = 0.f;
-    for (int i = lane_id(); i < W; i += 32) a = fmaf(ldf(Wg + (int64_t)j * W + i), xs[i], a);
-    a = warp_sum(a);
-    if (lane_id() == 0) gs[j] = gelu_tanh_f(a) * ldf(table + id * ld_table + col0 + j);
-  }
-  __syncthreads();
   float q = 0.f;
   for (int i = threadIdx.x; i < W; i += kRowThreads) {
-    float y = 0.f;
-    for (int j = 0; j < dim; ++j) y = fmaf(ldf(Wp + (int64_t)i * dim + j), gs[j], y);
-    q += y * y;
+    const float v = y[t * W + i];
+    q += v * v;
   }
   const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
-  for (int i = threadIdx.x; i < W; i += kRowThreads) {
-    float y = 0.f;
-    for (int j = 0; j < dim; ++j) y = fmaf(ldf(Wp + (int64_t)i * dim + j), gs[j], y);
-    resid[t * W + i] = xs[i] + y * rstd * ldf(nw + i);
-  }
+  for (int i = threadIdx.x; i < W; i += kRowThreads) resid[t * W + i] += y[t * W + i] * rstd * ldf(w + i);
 }
 
 }  // namespace seq
@@ -200,18 +200,21 @@ extern "C" int b200_seq_ff_clamped_gate(const void* gu, void* out, int dt, int64
   return B200_OK;
 }
 
-extern "C" int b200_seq_token_side(float* resid, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V,
-                                   const void* Wg, const void* Wp, const void* nw, int dt, int64_t T, int64_t W, float eps, void* stream) {
+extern "C" int b200_seq_side_gate(const float* a, const int64_t* ids, const void* table, int64_t ld_table, int64_t col0, int dim, int64_t V,
+                                  void* out, int dt, int64_t rows, void* stream) {
+  if (rows == 0 || dim == 0) return B200_OK;
+  int64_t blocks = (rows * dim + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((side_gate_kernel<E>), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, a, ids, (const E*)table,
+                                       ld_table, col0, dim, V, (E*)out, rows));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_rms_add(const float* y, const void* w, int dt, float* resid, int64_t T, int64_t W, float eps, void* stream) {
   if (T == 0) return B200_OK;
-  const size_t smem = (size_t)(W + dim) * 4;
-  if (smem > 160 * 1024) { b200_set_last_error("seq_token_side: row too wide"); return B200_ERR_ARG; }
-  cudaStream_t st = (cudaStream_t)stream;
-  B200_SEQ_DISPATCH(dt, E, {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(token_side_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); cfg = true; }
-    B200_LAUNCH((token_side_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), smem, st, resid, ids, (const E*)table, ld_table, col0, dim, V,
-                (const E*)Wg, (const E*)Wp, (const E*)nw, (int)W, eps);
-  });
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((rms_add_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, y, (const E*)w, resid,
+                                       (int)W, eps));
   b200_count_launches(1);
   return B200_OK;
 }

@@ -117,8 +117,8 @@ class _Norm(nn.Module):
     def forward(self, x):
         return ops.layernorm(x, self.w, self.b, self.eps)
 
-    def add_into(self, y, residual):
-        ops.layernorm_into_residual(y, self.w, self.b, self.eps, residual)
+    def add_into(self, y, residual, typed_copy: bool = False):
+        return ops.layernorm_into_residual(y, self.w, self.b, self.eps, residual, typed_copy)
 
 
 class FetotarLayer(nn.Module):
@@ -138,11 +138,11 @@ class FetotarLayer(nn.Module):
 
     def forward(self, x: torch.Tensor, input_ids, side_table, step: ops.RaggedStep, store, max_s: int) -> None:
         """advances the fp32 stream x in place"""
-        self.norm1b.add_into(self.mixer(self.norm1(x), step, store, max_s), x)
+        x_t = self.norm1b.add_into(self.mixer(self.norm1(x), step, store, max_s), x, typed_copy=self.mlp is None)
         if self.mlp is not None:
-            self.norm2b.add_into(self.mlp(self.norm2(x)), x)
-        ops.token_side(x, input_ids, side_table, self.index * self.side_dim, self.side_dim, self.side_gate, self.side_proj, self.side_norm,
-                       self.eps)
+            x_t = self.norm2b.add_into(self.mlp(self.norm2(x)), x, typed_copy=True)
+        ops.token_side(x, x_t, input_ids, side_table, self.index * self.side_dim, self.side_dim, self.side_gate, self.side_proj,
+                       self.side_norm, self.eps)
 
 
 class FetotarModel(nn.Module):

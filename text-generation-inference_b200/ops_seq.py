@@ -121,12 +121,16 @@ def layernorm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float) -> 
     return out
 
 
-def layernorm_into_residual(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, residual: torch.Tensor) -> None:
-    """residual (fp32, in place) += LayerNorm(x) * w + b."""
+def layernorm_into_residual(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, residual: torch.Tensor,
+                            typed_copy: bool = False) -> Optional[torch.Tensor]:
+    """residual (fp32, in place) += LayerNorm(x) * w + b.  typed_copy: also returns the updated residual in w's element type
+    (the input of the next projection); for float32 that is the residual itself."""
     _cuda(x, w, b, residual)
     assert x.is_contiguous() and residual.is_contiguous() and residual.dtype == torch.float32 and x.shape == residual.shape
-    _lib.check_seq(_lib.load_seq().b200_seq_layernorm(_ptr(x), _dt(x), _ptr(w), _ptr(b), _dt(w), None, _ptr(residual), x.shape[0],
+    copy = torch.empty(x.shape, dtype=w.dtype, device=x.device) if typed_copy and w.dtype != torch.float32 else None
+    _lib.check_seq(_lib.load_seq().b200_seq_layernorm(_ptr(x), _dt(x), _ptr(w), _ptr(b), _dt(w), _ptr(copy), _ptr(residual), x.shape[0],
                                                       x.shape[1], float(eps), _stream()), "seq_layernorm")
+    return (copy if copy is not None else residual) if typed_copy else None
 
 
 GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER = 0, 1, 2
@@ -160,15 +164,20 @@ def ff_clamped_gate(gate_up: torch.Tensor, limit: float, alpha: float = 1.702) -
     return out
 
 
-def token_side(residual: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int, dim: int, w_gate: torch.Tensor,
-               w_proj: torch.Tensor, norm_w: torch.Tensor, eps: float) -> None:
-    """residual (fp32, in place) += unit_rms(w_proj (gelu_tanh(w_gate x) * table[id, col0:col0+dim])) * norm_w."""
-    _cuda(residual, ids, table, w_gate, w_proj, norm_w)
-    assert residual.dtype == torch.float32 and residual.is_contiguous() and w_gate.is_contiguous() and w_proj.is_contiguous()
+def token_side(residual: torch.Tensor, residual_typed: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int, dim: int,
+               w_gate: torch.Tensor, w_proj: torch.Tensor, norm_w: torch.Tensor, eps: float) -> None:
+    """residual (fp32, in place) += unit_rms(w_proj (gelu_tanh(w_gate x) * table[id, col0:col0+dim])) * norm_w.  `residual_typed` is x
+    in the projections' element type (layernorm_into_residual(..., typed_copy=True))."""
+    _cuda(residual, residual_typed, ids, table, w_gate, w_proj, norm_w)
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
     T, W = residual.shape
-    _lib.check_seq(_lib.load_seq().b200_seq_token_side(_ptr(residual), _ptr(ids), _ptr(table), table.stride(0), col0, dim, table.shape[0],
-                                                       _ptr(w_gate), _ptr(w_proj), _ptr(norm_w), _dt(table), T, W, float(eps), _stream()),
-                   "seq_token_side")
+    lib = _lib.load_seq()
+    a = linear(residual_typed, w_gate, out_dtype=torch.float32)
+    g = torch.empty(T, dim, dtype=table.dtype, device=table.device)
+    _lib.check_seq(lib.b200_seq_side_gate(_ptr(a), _ptr(ids), _ptr(table), table.stride(0), col0, dim, table.shape[0], _ptr(g), _dt(table), T,
+                                          _stream()), "seq_side_gate")
+    y = linear(g, w_proj, out_dtype=torch.float32)
+    _lib.check_seq(lib.b200_seq_rms_add(_ptr(y), _ptr(norm_w), _dt(norm_w), _ptr(residual), T, W, float(eps), _stream()), "seq_rms_add")
 
 
 def latent_prepare(down: torch.Tensor, col_c: int, col_kr: int, q: torch.Tensor, q_head_stride: int, q_rot_off: int,
