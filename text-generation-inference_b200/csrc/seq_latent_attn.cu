@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(kHeadsPerBlock * 32) latent_attn_kernel(
 // registers.  Needs D % 16 == 0, R % 64 == 0, R <= 512; other shapes and float32 caches take latent_attn_kernel above.
 // ------------------------------------------------------------------------------------------------------------------------
 constexpr int kMmaKeys = 64, kMmaThreads = 128, kMmaPad = 8;
+static_assert(kMmaThreads == 2 * kMmaKeys, "the tile loader pairs two threads with a key row");
 
 template <int NTW>  // n-tiles (8 output columns each) per warp: R = 32 * NTW
 __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
@@ -195,15 +196,16 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
   const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), ps_addr = smem_u32(Ps);
   for (int j0 = j_lo; j0 <= p; j0 += kMmaKeys) {
     __syncthreads();  // everyone is done with the previous tile (and Qs is written, first time round)
-    for (int idx = threadIdx.x; idx < kMmaKeys * chunks; idx += kMmaThreads) {
-      const int row = idx / chunks, ch = idx % chunks;
-      const int j = j0 + row;
-      __nv_bfloat16* dst = Ks + row * DP + ch * 8;
+    {
+      // two threads per key row: one block-table lookup per thread and tile, then the row's 16-byte pieces alternate between them
+      const int row = threadIdx.x >> 1, j = j0 + row;
+      __nv_bfloat16* dst = Ks + row * DP;
       if (j <= p) {
-        const int64_t crow = (int64_t)table[j / page] * page + j % page;
-        cp_async_16(dst, cache + crow * D + ch * 8, true);
+        const __nv_bfloat16* src = cache + ((int64_t)table[j / page] * page + j % page) * D;
+        for (int ch = threadIdx.x & 1; ch < chunks; ch += 2) cp_async_16(dst + ch * 8, src + ch * 8, true);
       } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);  // finite: these rows meet p = 0
+        for (int ch = threadIdx.x & 1; ch < chunks; ch += 2)
+          *reinterpret_cast<uint4*>(dst + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: these rows meet p = 0
       }
     }
     cp_async_commit();

@@ -44,17 +44,23 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
   const int g = h / heads_per_group;
   const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
-  const int v = v0 + col;
-  const bool vok = v < P;
   const int t_begin = cu_q[b], t_end = cu_q[b + 1];
   if (t_begin >= t_end) return;
   const bool fresh = position_ids[t_begin] == 0;
   float* sp = state + ((int64_t)state_slots[b] * H + h) * N * P;
   float S[KMAX];
+  float* stage = dec + kChunk;  // [N][kCols + 1]: the state tile passes through shared memory so that global rows are read whole
+  if (!fresh) {
+    for (int idx = threadIdx.x; idx < N * kCols; idx += kScanThreads) {
+      const int n = idx / kCols, c = idx % kCols;
+      stage[n * (kCols + 1) + c] = (v0 + c < P) ? sp[(int64_t)n * P + v0 + c] : 0.f;
+    }
+    __syncthreads();
+  }
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
     const int n = ks + kSplit * i;
-    S[i] = (!fresh && vok && n < N) ? sp[(int64_t)n * P + v] : 0.f;
+    S[i] = (!fresh && n < N) ? stage[n * (kCols + 1) + col] : 0.f;
   }
   const float bias = ldf(dt_bias + h), A = expf(ldf(A_log + h)), Dh = ldf(Dskip + h);
   for (int t0 = t_begin; t0 < t_end; t0 += kChunk) {
@@ -97,12 +103,16 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
       if (v0 + c < P) y[(int64_t)(t0 + tt) * ld_y + h * P + v0 + c] = ys[idx];
     }
   }
-  if (vok) {
+  __syncthreads();
 #pragma unroll
-    for (int i = 0; i < KMAX; ++i) {
-      const int n = ks + kSplit * i;
-      if (n < N) sp[(int64_t)n * P + v] = S[i];
-    }
+  for (int i = 0; i < KMAX; ++i) {
+    const int n = ks + kSplit * i;
+    if (n < N) stage[n * (kCols + 1) + col] = S[i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < N * kCols; idx += kScanThreads) {
+    const int n = idx / kCols, c = idx % kCols;
+    if (v0 + c < P) sp[(int64_t)n * P + v0 + c] = stage[n * (kCols + 1) + c];
   }
 }
 
@@ -123,8 +133,6 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
   float* fg = ig + kChunk;              // [kChunk]
   const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kCols;
   const int col = threadIdx.x / kSplit, ks = threadIdx.x % kSplit;
-  const int v = v0 + col;
-  const bool vok = v < dv;
   const int t_begin = cu_q[b], t_end = cu_q[b + 1];
   if (t_begin >= t_end) return;
   const bool fresh = position_ids[t_begin] == 0;
@@ -132,10 +140,18 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
   float* Sp = S_state + (slot * H + h) * dk * dv;
   float* np = n_state + (slot * H + h) * dk;
   float S[KMAX], nn[KMAX];
+  float* stage = fg + kChunk;  // [dk][kCols + 1]: the state tile passes through shared memory so that global rows are read whole
+  if (!fresh) {
+    for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+      const int n = idx / kCols, c = idx % kCols;
+      stage[n * (kCols + 1) + c] = (v0 + c < dv) ? Sp[(int64_t)n * dv + v0 + c] : 0.f;
+    }
+    __syncthreads();
+  }
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
     const int n = ks + kSplit * i;
-    S[i] = (!fresh && vok && n < dk) ? Sp[(int64_t)n * dv + v] : 0.f;
+    S[i] = (!fresh && n < dk) ? stage[n * (kCols + 1) + col] : 0.f;
     nn[i] = (!fresh && n < dk) ? np[n] : 0.f;
   }
   float m = fresh ? 0.f : m_state[slot * H + h];
@@ -187,13 +203,19 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
       if (v0 + c < dv) y[(int64_t)(t0 + tt) * ld_y + h * dv + v0 + c] = ys[idx];
     }
   }
+  __syncthreads();
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
     const int n = ks + kSplit * i;
     if (n < dk) {
-      if (vok) Sp[(int64_t)n * dv + v] = S[i];
+      stage[n * (kCols + 1) + col] = S[i];
       if (blockIdx.z == 0 && col == 0) np[n] = nn[i];
     }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < dk * kCols; idx += kScanThreads) {
+    const int n = idx / kCols, c = idx % kCols;
+    if (v0 + c < dv) Sp[(int64_t)n * dv + v0 + c] = stage[n * (kCols + 1) + c];
   }
   if (blockIdx.z == 0 && threadIdx.x == 0) m_state[slot * H + h] = m;
 }
@@ -284,7 +306,9 @@ template <typename TP, int KMAX>
 static int launch_ssm(const float* xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* dt_raw, int64_t ld_dt, int col_dt,
                       const void* dt_bias, const void* A_log, const void* Dskip, float* state, const int32_t* state_slots, const int32_t* cu_q,
                       const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int P, int N, int hpg, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * kChunk * N + 2 * kChunk * kCols + 2 * kChunk) * 4;
+  const size_t smem = ((size_t)2 * kChunk * N + 2 * kChunk * kCols + 2 * kChunk + (size_t)N * (kCols + 1)) * 4;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(ssm_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); cfg = true; }
   dim3 grid((unsigned)B, (unsigned)H, (unsigned)((P + kCols - 1) / kCols));
   B200_LAUNCH((ssm_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, xbc, ld_xbc, col_x, col_B, col_C, dt_raw, ld_dt, col_dt,
               (const TP*)dt_bias, (const TP*)A_log, (const TP*)Dskip, state, state_slots, cu_q, position_ids, y, ld_y, H, P, N, hpg);
@@ -313,7 +337,9 @@ template <typename TP, int KMAX>
 static int launch_mlstm(const float* proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const void* i_bias, const void* f_bias,
                         float cap, float q_scale, float* S_state, float* n_state, float* m_state, const int32_t* state_slots, const int32_t* cu_q,
                         const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * kChunk * dk + 2 * kChunk * kCols + 2 * kChunk) * 4;
+  const size_t smem = ((size_t)2 * kChunk * dk + 2 * kChunk * kCols + 2 * kChunk + (size_t)dk * (kCols + 1)) * 4;
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(mlstm_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); cfg = true; }
   dim3 grid((unsigned)B, (unsigned)H, (unsigned)((dv + kCols - 1) / kCols));
   B200_LAUNCH((mlstm_scan_kernel<TP, KMAX>), grid, dim3(kScanThreads), smem, st, proj, ld, col_q, col_k, col_v, col_i, col_f, (const TP*)i_bias,
               (const TP*)f_bias, cap, q_scale, S_state, n_state, m_state, state_slots, cu_q, position_ids, y, ld_y, H, dk, dv);
