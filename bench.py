@@ -774,6 +774,14 @@ def run_hybrid_compare(args):
         for n, fn in saved.items():
             setattr(ops_seq, n, fn)
         model.kv_cache_manager.free_sequences(sids)
+        # the serving path: from_pb -> generate_token, plain greedy, replayed as one CUDA graph from the third step of the batch
+        with torch.inference_mode():
+            gbatch, _ = model.batch_type.from_pb(make_batch_pb(DB, DL, Wm + K + 8), model.tokenizer, torch.bfloat16, model.device, None, None, True)
+            model.generate_token(gbatch, first=True)
+            for _ in range(Wm):
+                model.generate_token(gbatch)
+            graph_ms = timed(lambda: model.generate_token(gbatch), K)
+            model.kv_cache_manager.free_sequences(gbatch.sequence_ids)
         la, ss, ml = raw["layers"][1]["mixer"], raw["layers"][2]["mixer"], raw["layers"][0]["mixer"]
         D, R, H = la["kv_rank"] + la["rot_dim"], la["kv_rank"], la["heads"]
         attn_flops = PB * (PL * (PL + 1) // 2) * H * (D + R) * 2
@@ -800,6 +808,7 @@ def run_hybrid_compare(args):
         kernels["linear decode (all projections)"] = {"ms": dec_ops["linear"], "of_measured_hbm": lin_w * 2 / (dec_ops["linear"] * 1e-3) / hbm}
         results.append({"model": f"fetotar-w{width}", "dtype": "bf16", "layers": 3, "prefill_tokens_per_s": PB * PL / (pre_ms * 1e-3),
                         "decode_tokens_per_s": DB / (dec_ms * 1e-3), "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms,
+                        "decode_graph_tokens_per_s": DB / (graph_ms * 1e-3), "decode_graph_ms_per_step": graph_ms,
                         "prefill_ms_by_op": {k: round(v, 4) for k, v in pre_ops.items()},
                         "decode_ms_by_op": {k: round(v, 4) for k, v in dec_ops.items()}, "kernels": kernels})
         del model, engine, weights
@@ -842,6 +851,11 @@ def run_hybrid_compare(args):
                 setattr(ops_f16, n, fn)
             os.environ.pop("B200_PY_FUSED_STEP", None)
             nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+            batch = nprefill(DB, DL, Wm + K + 8, keep=True)  # and as served: the graph-replayed step
+            for _ in range(Wm):
+                nmodel.generate_token(batch)
+            ngraph_ms = timed(lambda: nmodel.generate_token(batch), K)
+            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
         hd, nh = 128, width // 128
         nattn_flops = PB * 4 * (PL * PL // 2) * hd * nh
         nlin_w = 3 * (4 * width * width + 2 * width * 4 * width) + ncfg.vocab_size * width
@@ -858,6 +872,7 @@ def run_hybrid_compare(args):
         results.append({"model": wl, "dtype": "fp16", "layers": 3, "prefill_tokens_per_s": PB * PL / (npre_ms * 1e-3),
                         "decode_tokens_per_s": DB / (ndec_ms * 1e-3), "prefill_ms": npre_ms, "decode_ms_per_step": ndec_ms,
                         "decode_mode": "op by op (B200_PY_FUSED_STEP=0)",
+                        "decode_graph_tokens_per_s": DB / (ngraph_ms * 1e-3), "decode_graph_ms_per_step": ngraph_ms,
                         "prefill_ms_by_op": {k: round(v, 4) for k, v in npre_ops.items()},
                         "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()}, "kernels": nkernels})
         del nmodel

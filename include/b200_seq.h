@@ -47,10 +47,13 @@ int b200_seq_latent_prepare(const float* down, int64_t ld_down, int col_c, int c
                             int q_rot_off, const void* cnorm_w, const float* cos_t, const float* sin_t, const int64_t* position_ids,
                             const int64_t* slot_mapping, void* cache, int dt, float* q_abs, int64_t T, int H, int R, int r, int rot_dims,
                             float eps, void* stream);
-/* out[t, h, :R] = sum_j softmax_j((q_abs[t, h] . cache_row(j)) * scale) cache_row(j)[:R], j over (p - window, p] of t's sequence */
+/* out[t, h, :R] = sum_j softmax_j((q_abs[t, h] . cache_row(j)) * scale) cache_row(j)[:R], j over (p - window, p] of t's sequence.
+ * b200_seq_latent_attn_splits: over how many blocks the tensor-core kernel should split each token's keys for this shape (0: the
+ * shape takes the plain kernel) and the fp32 workspace (`partial`) that takes; partial NULL / nsplit <= 1: no split */
+int b200_seq_latent_attn_splits(int dt, int64_t Tq, int H, int R, int r, int64_t* workspace_floats);
 int b200_seq_latent_attn(const float* q_abs, const void* cache, int dt, const int32_t* block_table, int64_t bt_stride,
                          const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int R, int r, int window,
-                         float scale, int page, void* stream);
+                         float scale, int page, float* partial, int nsplit, void* stream);
 /* SiLU(depth-wise causal convolution) of columns [col0, col0 + C) of u; conv_state [slots, taps - 1, C] read and advanced */
 int b200_seq_causal_conv_silu(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt,
                               float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,

@@ -137,7 +137,8 @@ SEQ_SIGNATURES = {
     "b200_seq_side_gate": (_I, [_P, _P, _P, _L, _L, _I, _L, _P, _I, _L, _P]),
     "b200_seq_rms_add": (_I, [_P, _P, _I, _P, _L, _L, _F, _P]),
     "b200_seq_latent_prepare": (_I, [_P, _L, _I, _I, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _F, _P]),
-    "b200_seq_latent_attn": (_I, [_P, _P, _I, _P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _P]),
+    "b200_seq_latent_attn_splits": (_I, [_I, _L, _I, _I, _I, ctypes.POINTER(c_int64)]),
+    "b200_seq_latent_attn": (_I, [_P, _P, _I, _P, _L, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _P, _I, _P]),
     "b200_seq_causal_conv_silu": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _L, _I, _P]),
     "b200_seq_ssm_scan": (_I, [_P, _L, _I, _I, _I, _P, _L, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
     "b200_seq_mlstm_scan": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _F, _F, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P]),

@@ -164,7 +164,7 @@ template <int NTW>  // n-tiles (8 output columns each) per warp: R = 32 * NTW
 __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
     const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_table, int64_t bt_stride,
     const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H, int R, int D, int window,
-    float scale, int page) {
+    float scale, int page, float* __restrict__ partial) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -180,7 +180,13 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
   const int w = warp_id(), lane = lane_id();
   const int b = seq_of_token[t];
   const int p = (int)position_ids[t];
-  const int j_lo = max(0, p - window + 1);
+  const int j_first = max(0, p - window + 1);
+  // gridDim.z > 1: the token's key tiles are dealt out in contiguous runs to gridDim.z blocks, whose (max, sum, unnormalised O) per
+  // head are merged by latent_attn_merge_kernel; a block whose run is empty records an empty partial
+  const int n_tiles = (p - j_first + kMmaKeys) / kMmaKeys;
+  const int per_split = (n_tiles + gridDim.z - 1) / gridDim.z;
+  const int j_lo = j_first + (int)blockIdx.z * per_split * kMmaKeys;
+  const int j_hi = min(p, j_lo + per_split * kMmaKeys - 1);
   const int32_t* table = block_table + (int64_t)b * bt_stride;
   for (int idx = threadIdx.x; idx < 16 * D; idx += kMmaThreads) {
     const int row = idx / D, d = idx % D;
@@ -194,7 +200,7 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
   for (int i = 0; i < NTW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const int chunks = D / 8;  // 16-byte pieces of a cache row
   const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), ps_addr = smem_u32(Ps);
-  for (int j0 = j_lo; j0 <= p; j0 += kMmaKeys) {
+  for (int j0 = j_lo; j0 <= j_hi; j0 += kMmaKeys) {
     __syncthreads();  // everyone is done with the previous tile (and Qs is written, first time round)
     {
       // two threads per key row: one block-table lookup per thread and tile, then the row's 16-byte pieces alternate between them
@@ -306,6 +312,25 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
       }
     }
   }
+  if (gridDim.z > 1) {
+    // partial [token][head group][split][16 rows][R + 2]: unnormalised O, then the running max and sum
+    float* base = partial + ((((int64_t)t * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z) * 16) * (R + 2);
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+      const int col = (w * NTW + nt) * 8 + cq;
+      base[r0 * (R + 2) + col] = o[nt][0];
+      base[r0 * (R + 2) + col + 1] = o[nt][1];
+      base[(r0 + 8) * (R + 2) + col] = o[nt][2];
+      base[(r0 + 8) * (R + 2) + col + 1] = o[nt][3];
+    }
+    if (w == 0 && (lane & 3) == 0) {
+      base[r0 * (R + 2) + R] = m_run[0];
+      base[r0 * (R + 2) + R + 1] = l_run[0];
+      base[(r0 + 8) * (R + 2) + R] = m_run[1];
+      base[(r0 + 8) * (R + 2) + R + 1] = l_run[1];
+    }
+    return;
+  }
   const float inv0 = 1.f / l_run[0], inv1 = 1.f / l_run[1];
 #pragma unroll
   for (int nt = 0; nt < NTW; ++nt) {
@@ -320,6 +345,34 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(
       dst[0] = o[nt][2] * inv1;
       dst[1] = o[nt][3] * inv1;
     }
+  }
+}
+
+// out[t, h] = sum_z e^(m_z - M) O_z / sum_z e^(m_z - M) l_z over the splits of latent_attn_mma_kernel; one warp per (token, head)
+__global__ void latent_attn_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t Tq, int H, int R, int groups, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x / 32) + warp_id();
+  if (wid >= Tq * H) return;
+  const int64_t t = wid / H;
+  const int h = (int)(wid % H), g = h / 16, row = h % 16, lane = lane_id();
+  const float* base = partial + (((t * groups + g) * nsplit) * 16 + row) * (R + 2);
+  const int64_t zs = (int64_t)16 * (R + 2);
+  float M = -INFINITY;
+  for (int z = 0; z < nsplit; ++z) M = fmaxf(M, base[z * zs + R]);
+  float den = 0.f;
+  for (int z = 0; z < nsplit; ++z) {
+    const float mz = base[z * zs + R];
+    if (mz > -INFINITY) den += expf(mz - M) * base[z * zs + R + 1];
+  }
+  const float inv = 1.f / den;
+  for (int c = lane; c < R; c += 32) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) {
+      const float mz = base[z * zs + R];
+      if (mz > -INFINITY) acc += expf(mz - M) * base[z * zs + c];
+    }
+    out[(t * H + h) * R + c] = acc * inv;
   }
 }
 
@@ -357,9 +410,23 @@ static int launch_latent_attn(const float* q_abs, const void* cache, const int32
 }
 
 // q_abs [Tq, H, D] fp32; cache [blocks, page, D] of type dt; out [Tq, H, R] fp32.  window <= 0: every earlier token is visible.
+// Blocks the tensor-core kernel should split every token's keys over (1 = no split), and the fp32 workspace that needs: few tokens
+// (decoding) leave most SMs idle with one block per (token, 16 heads).  0 when the shape takes the plain kernel.
+extern "C" int b200_seq_latent_attn_splits(int dt, int64_t Tq, int H, int R, int r, int64_t* workspace_floats) {
+  const int D = R + r;
+  if (workspace_floats) *workspace_floats = 0;
+  if (!(dt == B200_DT_BF16 && D % 16 == 0 && R % 64 == 0 && R <= 512)) return 0;
+  const int64_t blocks = Tq * ((H + 15) / 16);
+  int64_t n = (2 * 148) / (blocks > 0 ? blocks : 1);
+  n = n < 1 ? 1 : (n > 8 ? 8 : n);
+  if (n > 1 && workspace_floats) *workspace_floats = blocks * n * 16 * (R + 2);
+  return (int)n;
+}
+
+// `partial` / nsplit: from b200_seq_latent_attn_splits (NULL / <= 1: no split).
 extern "C" int b200_seq_latent_attn(const float* q_abs, const void* cache, int dt, const int32_t* block_table, int64_t bt_stride,
                                     const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int R, int r,
-                                    int window, float scale, int page, void* stream) {
+                                    int window, float scale, int page, float* partial, int nsplit, void* stream) {
   if (Tq == 0) return B200_OK;
   const int D = R + r;
   if (window <= 0) window = 0x3fffffff;
@@ -369,14 +436,18 @@ extern "C" int b200_seq_latent_attn(const float* q_abs, const void* cache, int d
   if (use_mma && dt == B200_DT_BF16 && D % 16 == 0 && R % 64 == 0 && R <= 512 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
     const int ntw = R / 32;
     const size_t smem = ((size_t)(16 + kMmaKeys) * (D + kMmaPad) + 16 * (kMmaKeys + kMmaPad)) * 2 + 128 * 4;
-    dim3 grid((unsigned)Tq, (unsigned)((H + 15) / 16));
+    if (!partial || nsplit < 1) nsplit = 1;
+    dim3 grid((unsigned)Tq, (unsigned)((H + 15) / 16), (unsigned)nsplit);
 #define LAM(N)                                                                                                                        \
   do {                                                                                                                                \
     static bool cfg = false;                                                                                                          \
     if (!cfg) { cudaFuncSetAttribute(latent_attn_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
     B200_LAUNCH((latent_attn_mma_kernel<N>), grid, dim3(kMmaThreads), smem, st, q_abs, (const __nv_bfloat16*)cache, block_table, bt_stride, \
-                seq_of_token, position_ids, out, H, R, D, window, scale, page);                                                       \
-    b200_count_launches(1);                                                                                                           \
+                seq_of_token, position_ids, out, H, R, D, window, scale, page, partial);                                              \
+    if (nsplit > 1)                                                                                                                   \
+      B200_LAUNCH(latent_attn_merge_kernel, dim3((unsigned)((Tq * H + 3) / 4)), dim3(128), 0, st, (const float*)partial, out, Tq, H, R, \
+                  (int)grid.y, nsplit);                                                                                              \
+    b200_count_launches(nsplit > 1 ? 2 : 1);                                                                                          \
     return B200_OK;                                                                                                                   \
   } while (0)
     switch (ntw) {

@@ -394,7 +394,7 @@ class FlashCausalLM(Model):
         if st is None or st["key"] != key:
             V = self.model.lm_head.linear.weight.shape[0]
             st = dict(key=key, next_ids=torch.empty(B, dtype=torch.int64, device=self.device),
-                      logits=torch.empty(B, V, dtype=torch.float16, device=self.device),
+                      logits=torch.empty(B, V, dtype=getattr(self.model, "logits_dtype", torch.float16), device=self.device),
                       banned=torch.full((B,), -1, dtype=torch.int64, device=self.device), banned_host=[-1] * B,
                       steps=0, graph=None, max_s_cap=0)
             tp = getattr(self.engine, "world_size", 1)

@@ -6,6 +6,7 @@ soft-max, recurrences, states and the residual stream are fp32 in both.  CUDA te
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from dataclasses import dataclass
 from typing import Optional
@@ -53,6 +54,7 @@ class RaggedStep:
 
 
 _TC_GEMM = os.getenv("B200_SEQ_TC_GEMM", "1") != "0"
+_ATTN_SPLIT = os.getenv("B200_SEQ_ATTN_SPLIT", "1") != "0"
 _gemm_ws = {}
 
 
@@ -200,9 +202,14 @@ def latent_attn(q_abs: torch.Tensor, cache: torch.Tensor, step: RaggedStep, R: i
     T, H, D = q_abs.shape
     assert D == R + r and cache.shape[-1] == D and q_abs.is_contiguous() and cache.is_contiguous()
     out = torch.empty(T, H, R, dtype=torch.float32, device=q_abs.device)
-    _lib.check_seq(_lib.load_seq().b200_seq_latent_attn(
+    lib = _lib.load_seq()
+    need = ctypes.c_int64(0)
+    nsplit = lib.b200_seq_latent_attn_splits(_dt(cache), T, H, R, r, ctypes.byref(need)) if _ATTN_SPLIT else 1
+    partial = torch.empty(need.value, dtype=torch.float32, device=q_abs.device) if nsplit > 1 else None
+    _lib.check_seq(lib.b200_seq_latent_attn(
         _ptr(q_abs), _ptr(cache), _dt(cache), _ptr(step.block_table), step.block_table.stride(0), _ptr(step.seq_of_token),
-        _ptr(step.position_ids), _ptr(out), T, H, R, r, int(window), float(scale), cache.shape[1], _stream()), "seq_latent_attn")
+        _ptr(step.position_ids), _ptr(out), T, H, R, r, int(window), float(scale), cache.shape[1], _ptr(partial), nsplit, _stream()),
+        "seq_latent_attn")
     return out
 
 
