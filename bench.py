@@ -694,6 +694,37 @@ def _by_op(log):
     return out
 
 
+def _traced_decode_step(model, batch, lib):
+    """device time of every kernel of one fused decode step: the step is captured in a graph of its own with a time stamp after
+    every launch of the library (host latency is out of the picture, L2 as in the served step).  -> ({kernel: us}, total us)"""
+    import re
+    import torch
+    cap = 4096
+    buf = torch.zeros(cap, dtype=torch.int64, device=model.device)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        lib.b200_debug_step_trace(buf.data_ptr(), cap)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            lib.b200_debug_step_trace_begin(torch.cuda.current_stream().cuda_stream)
+            model._run_fused_step(batch, batch._fused, False)
+        names_buf = ctypes.create_string_buffer(1 << 20)
+        n = lib.b200_debug_step_trace_names(names_buf, len(names_buf))
+        lib.b200_debug_step_trace(None, 0)
+        for _ in range(3):
+            g.replay()
+        side.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    names = names_buf.value.decode().strip().split("\n")
+    t = buf[:n].cpu().tolist()
+    out = {}
+    for i in range(1, n):
+        k = re.sub(r"<.*", "", names[i].replace("b200::", "").replace("seq::", "").strip("()"))
+        out[k] = out.get(k, 0.0) + (t[i] - t[i - 1]) / 1e3
+    return out, (t[n - 1] - t[0]) / 1e3
+
+
 def run_hybrid_compare(args):
     """Fetotar (bfloat16) beside GPT-NeoX (fp16) at equal width and depth, random weights: prefill of 4 x 1024 tokens and decode of
     32 sequences at context 1024.  Per model: tokens/s through the engine's own step (device time by CUDA events, L2 flushed
@@ -781,6 +812,8 @@ def run_hybrid_compare(args):
             for _ in range(Wm):
                 model.generate_token(gbatch)
             graph_ms = timed(lambda: model.generate_token(gbatch), K)
+            from tgis_b200 import _lib as _libmod
+            dec_k, dec_total = _traced_decode_step(model, gbatch, _libmod.load_seq())
             model.kv_cache_manager.free_sequences(gbatch.sequence_ids)
         la, ss, ml = raw["layers"][1]["mixer"], raw["layers"][2]["mixer"], raw["layers"][0]["mixer"]
         D, R, H = la["kv_rank"] + la["rot_dim"], la["kv_rank"], la["heads"]
@@ -789,12 +822,12 @@ def run_hybrid_compare(args):
         kernels = {
             "latent_attn prefill": {"ms": pre_ops["latent_attn"], "tflops": attn_flops / pre_ops["latent_attn"] / 1e9,
                                     "of_measured_tensor": attn_flops / (pre_ops["latent_attn"] * 1e-3) / tens},
-            "latent_attn decode": {"ms": dec_ops["latent_attn"], "gbs": DB * ctx * D * 2 / dec_ops["latent_attn"] / 1e6,
-                                   "of_measured_hbm": DB * ctx * D * 2 / (dec_ops["latent_attn"] * 1e-3) / hbm},
-            "ssm_scan decode": {"ms": dec_ops["ssm_scan"], "of_measured_hbm":
-                                DB * ss["heads"] * ss["state"] * ss["vdim"] * 8 / (dec_ops["ssm_scan"] * 1e-3) / hbm},
-            "mlstm_scan decode": {"ms": dec_ops["mlstm_scan"], "of_measured_hbm":
-                                  DB * ml["heads"] * ml["dim"] * ml["vdim"] * 8 / (dec_ops["mlstm_scan"] * 1e-3) / hbm},
+            "latent_attn decode": {"us": dec_k.get("latent_attn_mma_kernel", 0.0) + dec_k.get("latent_attn_merge_kernel", 0.0), "of_measured_hbm":
+                                   DB * ctx * D * 2 / ((dec_k.get("latent_attn_mma_kernel", 0.0) + dec_k.get("latent_attn_merge_kernel", 0.0)) * 1e-6) / hbm},
+            "ssm_scan decode": {"us": dec_k["ssm_scan_kernel"], "of_measured_hbm":
+                                DB * ss["heads"] * ss["state"] * ss["vdim"] * 8 / (dec_k["ssm_scan_kernel"] * 1e-6) / hbm},
+            "mlstm_scan decode": {"us": dec_k["mlstm_scan_kernel"], "of_measured_hbm":
+                                  DB * ml["heads"] * ml["dim"] * ml["vdim"] * 8 / (dec_k["mlstm_scan_kernel"] * 1e-6) / hbm},
             "ssm_scan prefill": {"ms": pre_ops["ssm_scan"], "tokens_per_s": PB * PL / (pre_ops["ssm_scan"] * 1e-3)},
             "mlstm_scan prefill": {"ms": pre_ops["mlstm_scan"], "tokens_per_s": PB * PL / (pre_ops["mlstm_scan"] * 1e-3)},
         }
@@ -805,12 +838,14 @@ def run_hybrid_compare(args):
                     and not n.startswith("side") and ".side." not in n)
         lin_flops = 2 * PB * PL * (lin_w - shapes["head"][0] * shapes["head"][1]) + 2 * PB * shapes["head"][0] * shapes["head"][1]
         kernels["linear prefill (all projections)"] = {"ms": pre_ops["linear"], "of_measured_tensor": lin_flops / (pre_ops["linear"] * 1e-3) / tens}
-        kernels["linear decode (all projections)"] = {"ms": dec_ops["linear"], "of_measured_hbm": lin_w * 2 / (dec_ops["linear"] * 1e-3) / hbm}
+        kernels["linear decode (tcgen05 projections)"] = {"us": dec_k["gemm_f16_kernel"], "of_measured_hbm": lin_w * 2 / (dec_k["gemm_f16_kernel"] * 1e-6) / hbm}
         results.append({"model": f"fetotar-w{width}", "dtype": "bf16", "layers": 3, "prefill_tokens_per_s": PB * PL / (pre_ms * 1e-3),
                         "decode_tokens_per_s": DB / (dec_ms * 1e-3), "prefill_ms": pre_ms, "decode_ms_per_step": dec_ms,
                         "decode_graph_tokens_per_s": DB / (graph_ms * 1e-3), "decode_graph_ms_per_step": graph_ms,
                         "prefill_ms_by_op": {k: round(v, 4) for k, v in pre_ops.items()},
-                        "decode_ms_by_op": {k: round(v, 4) for k, v in dec_ops.items()}, "kernels": kernels})
+                        "decode_ms_by_op": {k: round(v, 4) for k, v in dec_ops.items()},
+                        "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(dec_k.items(), key=lambda kv: -kv[1])},
+                        "decode_graph_traced_us": dec_total, "kernels": kernels})
         del model, engine, weights
         gc.collect()
         torch.cuda.empty_cache()
@@ -855,6 +890,8 @@ def run_hybrid_compare(args):
             for _ in range(Wm):
                 nmodel.generate_token(batch)
             ngraph_ms = timed(lambda: nmodel.generate_token(batch), K)
+            from tgis_b200 import _lib as _libmod
+            ndec_k, ndec_total = _traced_decode_step(nmodel, batch, _libmod.load())
             nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
         hd, nh = 128, width // 128
         nattn_flops = PB * 4 * (PL * PL // 2) * hd * nh
@@ -862,19 +899,22 @@ def run_hybrid_compare(args):
         nkernels = {
             "attn_prefill_varlen": {"ms": npre_ops.get("attn_prefill_varlen", 0.0),
                                     "of_measured_tensor": nattn_flops / (max(npre_ops.get("attn_prefill_varlen", 0.0), 1e-9) * 1e-3) / tens},
-            "attn_decode_paged": {"ms": ndec_ops.get("attn_decode_paged", 0.0), "of_measured_hbm":
-                                  3 * DB * ctx * 2 * nh * hd * 2 / (max(ndec_ops.get("attn_decode_paged", 0.0), 1e-9) * 1e-3) / hbm},
+            "attn_decode_paged": {"us": ndec_k.get("attn_decode_paged_kernel", 0.0) + ndec_k.get("attn_decode_combine_kernel", 0.0), "of_measured_hbm":
+                                  3 * DB * ctx * 2 * nh * hd * 2
+                                  / ((ndec_k.get("attn_decode_paged_kernel", 1e-9) + ndec_k.get("attn_decode_combine_kernel", 0.0)) * 1e-6) / hbm},
             "gemm_f16 prefill (all projections)": {"ms": npre_ops["gemm_f16"], "of_measured_tensor":
                                                    (2 * PB * PL * (nlin_w - ncfg.vocab_size * width) + 2 * PB * ncfg.vocab_size * width)
                                                    / (npre_ops["gemm_f16"] * 1e-3) / tens},
-            "gemm_f16 decode (all projections)": {"ms": ndec_ops["gemm_f16"], "of_measured_hbm": nlin_w * 2 / (ndec_ops["gemm_f16"] * 1e-3) / hbm},
+            "gemm_f16 decode (all projections)": {"us": ndec_k["gemm_f16_kernel"], "of_measured_hbm": nlin_w * 2 / (ndec_k["gemm_f16_kernel"] * 1e-6) / hbm},
         }
         results.append({"model": wl, "dtype": "fp16", "layers": 3, "prefill_tokens_per_s": PB * PL / (npre_ms * 1e-3),
                         "decode_tokens_per_s": DB / (ndec_ms * 1e-3), "prefill_ms": npre_ms, "decode_ms_per_step": ndec_ms,
                         "decode_mode": "op by op (B200_PY_FUSED_STEP=0)",
                         "decode_graph_tokens_per_s": DB / (ngraph_ms * 1e-3), "decode_graph_ms_per_step": ngraph_ms,
                         "prefill_ms_by_op": {k: round(v, 4) for k, v in npre_ops.items()},
-                        "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()}, "kernels": nkernels})
+                        "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()},
+                        "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(ndec_k.items(), key=lambda kv: -kv[1])},
+                        "decode_graph_traced_us": ndec_total, "kernels": nkernels})
         del nmodel
         gc.collect()
         torch.cuda.empty_cache()

@@ -145,7 +145,7 @@ SEQ_SIGNATURES = {
 }
 _SEQ_SHARED = ("b200_last_error", "b200_cuda_peek_error", "b200_launch_count", "b200_kv_alloc_create", "b200_kv_alloc_destroy",
                "b200_kv_alloc_num_free", "b200_kv_alloc_take", "b200_kv_alloc_release", "b200_decode_advance", "b200_gemm_bf16",
-               "b200_gemm_workspace_bytes_max")
+               "b200_gemm_workspace_bytes_max", "b200_debug_step_trace", "b200_debug_step_trace_begin", "b200_debug_step_trace_names")
 
 _lib = None
 _seq_lib = None

@@ -358,20 +358,25 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ partial, floa
   const int h = (int)(wid % H), g = h / 16, row = h % 16, lane = lane_id();
   const float* base = partial + (((t * groups + g) * nsplit) * 16 + row) * (R + 2);
   const int64_t zs = (int64_t)16 * (R + 2);
-  float M = -INFINITY;
-  for (int z = 0; z < nsplit; ++z) M = fmaxf(M, base[z * zs + R]);
+  constexpr int kMaxSplit = 8;
+  float M = -INFINITY, wz[kMaxSplit];
+#pragma unroll
+  for (int z = 0; z < kMaxSplit; ++z) {
+    wz[z] = z < nsplit ? base[z * zs + R] : -INFINITY;
+    M = fmaxf(M, wz[z]);
+  }
   float den = 0.f;
-  for (int z = 0; z < nsplit; ++z) {
-    const float mz = base[z * zs + R];
-    if (mz > -INFINITY) den += expf(mz - M) * base[z * zs + R + 1];
+#pragma unroll
+  for (int z = 0; z < kMaxSplit; ++z) {
+    wz[z] = wz[z] > -INFINITY ? expf(wz[z] - M) : 0.f;  // an empty run carries no weight
+    if (z < nsplit) den += wz[z] * base[z * zs + R + 1];
   }
   const float inv = 1.f / den;
   for (int c = lane; c < R; c += 32) {
     float acc = 0.f;
-    for (int z = 0; z < nsplit; ++z) {
-      const float mz = base[z * zs + R];
-      if (mz > -INFINITY) acc += expf(mz - M) * base[z * zs + c];
-    }
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z)
+      if (z < nsplit) acc = fmaf(wz[z], base[z * zs + c], acc);
     out[(t * H + h) * R + c] = acc * inv;
   }
 }

@@ -61,32 +61,30 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const TX* __rest
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kRowThreads) group_rmsnorm_gate_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ gate,
                                                                          int64_t ldg, int gate_kind, const TP* __restrict__ w, int groups, int n,
-                                                                         float eps, TO* __restrict__ out, int64_t ldo) {
+                                                                         int C, float eps, TO* __restrict__ out, int64_t ldo) {
+  // grid (rows, parts): a part is one group of n columns (groups > 0) or a run of n columns of an un-normalised row (groups == 0)
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[32];
   const int64_t t = blockIdx.x;
-  const int ng = groups > 0 ? groups : 1;
-  for (int g = 0; g < ng; ++g) {
+  const int c0 = blockIdx.y * n, c1 = min(C, c0 + n);
+  float rstd = 1.f;
+  if (groups > 0) {
     float q = 0.f;
-    if (groups > 0) {
-      for (int i = threadIdx.x; i < n; i += kRowThreads) {
-        float v = x[t * ldx + g * n + i];
-        if (gate_kind == 1) v *= silu_f(gate[t * ldg + g * n + i]);
-        q += v * v;
-      }
-      q = block_sum(q, red);
-    }
-    const float rstd = groups > 0 ? 1.f / sqrtf(q / n + eps) : 1.f;
-    for (int i = threadIdx.x; i < n; i += kRowThreads) {
-      const int c = g * n + i;
+    for (int c = c0 + threadIdx.x; c < c1; c += kRowThreads) {
       float v = x[t * ldx + c];
       if (gate_kind == 1) v *= silu_f(gate[t * ldg + c]);
-      v *= rstd;
-      if (w) v *= ldf(w + c);
-      if (gate_kind == 2) v *= sigmoid_f(gate[t * ldg + c]);
-      stf(out + t * ldo + c, v);
+      q += v * v;
     }
+    rstd = 1.f / sqrtf(block_sum(q, red) / n + eps);
+  }
+  for (int c = c0 + threadIdx.x; c < c1; c += kRowThreads) {
+    float v = x[t * ldx + c];
+    if (gate_kind == 1) v *= silu_f(gate[t * ldg + c]);
+    v *= rstd;
+    if (w) v *= ldf(w + c);
+    if (gate_kind == 2) v *= sigmoid_f(gate[t * ldg + c]);
+    stf(out + t * ldo + c, v);
   }
 }
 
@@ -178,9 +176,12 @@ extern "C" int b200_seq_group_rmsnorm_gate(const float* x, int64_t ldx, const fl
   if (T == 0) return B200_OK;
   if (gate_kind != 0 && gate == nullptr) { b200_set_last_error("seq_group_rmsnorm_gate: gate missing"); return B200_ERR_ARG; }
   cudaStream_t st = (cudaStream_t)stream;
+  const int C = groups > 0 ? groups * n : n;
+  const int part = groups > 0 ? n : 2048;
+  const dim3 grid((unsigned)T, (unsigned)((C + part - 1) / part));
 #define GN_LAUNCH(TP, TO)                                                                                                                   \
-  B200_LAUNCH((group_rmsnorm_gate_kernel<TP, TO>), dim3((unsigned)T), dim3(kRowThreads), 0, st, x, ldx, gate, ldg, gate_kind, (const TP*)w, \
-              groups, n, eps, (TO*)out, ldo)
+  B200_LAUNCH((group_rmsnorm_gate_kernel<TP, TO>), grid, dim3(kRowThreads), 0, st, x, ldx, gate, ldg, gate_kind, (const TP*)w, groups, part, \
+              C, eps, (TO*)out, ldo)
   if (w_dt == B200_DT_F32 && out_dt == B200_DT_F32) GN_LAUNCH(float, float);
   else if (w_dt == B200_DT_BF16 && out_dt == B200_DT_BF16) GN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (w_dt == B200_DT_BF16 && out_dt == B200_DT_F32) GN_LAUNCH(__nv_bfloat16, float);
