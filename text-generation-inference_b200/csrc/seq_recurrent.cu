@@ -9,8 +9,8 @@
 //
 // One block owns (sequence, head, 32 value columns) and walks the sequence's tokens of this step in order, whether they are a
 // whole prompt, a portion of one or a single decoded token: the arithmetic per token is the same in every case, so the state
-// and the outputs do not depend on how a sequence was cut into steps.  A thread holds a run of consecutive state rows of one
-// column in registers; 8 neighbouring lanes (the column's runs) reduce the read-out.  A sequence whose first token of the step is at position 0
+// and the outputs do not depend on how a sequence was cut into steps.  A thread holds a column's state entries for every 8th
+// state row in registers; 8 neighbouring lanes reduce the read-out.  A sequence whose first token of the step is at position 0
 // starts from a zero state and never reads its (possibly reused) slot.
 #include "seq_common.cuh"
 
@@ -34,13 +34,10 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
     int64_t ld_y, int H, int P, int N, int heads_per_group) {
   pdl_launch_dependents();
   pdl_wait();
-  // a lane owns KMAX consecutive state rows; its B / C values sit in one padded run of shared memory, read as float4 without
-  // bank conflicts (runs are KMAX + 4 floats apart)
-  constexpr int CH = KMAX + 4, NP = kSplit * CH;
-  extern __shared__ __align__(16) float sm[];
-  float* Bs = sm;                      // [kChunk][NP]
-  float* Cs = Bs + kChunk * NP;        // [kChunk][NP]
-  float* xs = Cs + kChunk * NP;        // [kChunk][kCols]
+  extern __shared__ float sm[];
+  float* Bs = sm;                      // [kChunk][N]
+  float* Cs = Bs + kChunk * N;         // [kChunk][N]
+  float* xs = Cs + kChunk * N;         // [kChunk][kCols]
   float* ys = xs + kChunk * kCols;     // [kChunk][kCols]
   float* dts = ys + kChunk * kCols;    // [kChunk]
   float* dec = dts + kChunk;           // [kChunk]
@@ -62,7 +59,7 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
   }
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
-    const int n = ks * KMAX + i;
+    const int n = ks + kSplit * i;
     S[i] = (!fresh && n < N) ? stage[n * (kCols + 1) + col] : 0.f;
   }
   const float bias = ldf(dt_bias + h), A = expf(ldf(A_log + h)), Dh = ldf(Dskip + h);
@@ -72,9 +69,8 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
     for (int idx = threadIdx.x; idx < nt * N; idx += kScanThreads) {
       const int tt = idx / N, n = idx % N;
       const float* row = xbc + (int64_t)(t0 + tt) * ld_xbc;
-      const int at = tt * NP + n + (n / KMAX) * 4;
-      Bs[at] = row[col_B + g * N + n];
-      Cs[at] = row[col_C + g * N + n];
+      Bs[tt * N + n] = row[col_B + g * N + n];
+      Cs[tt * N + n] = row[col_C + g * N + n];
     }
     for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
       const int tt = idx / kCols, c = idx % kCols;
@@ -90,19 +86,12 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
       const float a = dec[tt], xv = xs[tt * kCols + col];
       const float coef = dts[tt] * xv;
       float part = 0.f;
-      const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP + ks * CH);
-      const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * NP + ks * CH);
 #pragma unroll
-      for (int i4 = 0; i4 < KMAX / 4; ++i4) {
-        const float4 bq = b4[i4], cq = c4[i4];
-        const float bv[4] = {bq.x, bq.y, bq.z, bq.w}, cv[4] = {cq.x, cq.y, cq.z, cq.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = i4 * 4 + e;
-          if (ks * KMAX + i < N) {
-            S[i] = fmaf(a, S[i], coef * bv[e]);
-            part = fmaf(S[i], cv[e], part);
-          }
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < N) {
+          S[i] = fmaf(a, S[i], coef * Bs[tt * N + n]);
+          part = fmaf(S[i], Cs[tt * N + n], part);
         }
       }
       part = group8_sum(part);
@@ -117,7 +106,7 @@ __global__ void __launch_bounds__(kScanThreads) ssm_scan_kernel(
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
-    const int n = ks * KMAX + i;
+    const int n = ks + kSplit * i;
     if (n < N) stage[n * (kCols + 1) + col] = S[i];
   }
   __syncthreads();
@@ -135,11 +124,10 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
     int64_t ld_y, int H, int dk, int dv) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int CH = KMAX + 4, NP = kSplit * CH;  // padded runs of a lane's KMAX consecutive key rows (see ssm_scan_kernel)
-  extern __shared__ __align__(16) float sm[];
-  float* qs = sm;                       // [kChunk][NP]
-  float* kk = qs + kChunk * NP;         // [kChunk][NP]
-  float* vs = kk + kChunk * NP;         // [kChunk][kCols]
+  extern __shared__ float sm[];
+  float* qs = sm;                       // [kChunk][dk]
+  float* kk = qs + kChunk * dk;         // [kChunk][dk]
+  float* vs = kk + kChunk * dk;         // [kChunk][kCols]
   float* ys = vs + kChunk * kCols;      // [kChunk][kCols]
   float* ig = ys + kChunk * kCols;      // [kChunk]
   float* fg = ig + kChunk;              // [kChunk]
@@ -162,7 +150,7 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
   }
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
-    const int n = ks * KMAX + i;
+    const int n = ks + kSplit * i;
     S[i] = (!fresh && n < dk) ? stage[n * (kCols + 1) + col] : 0.f;
     nn[i] = (!fresh && n < dk) ? np[n] : 0.f;
   }
@@ -174,9 +162,8 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
     for (int idx = threadIdx.x; idx < nt * dk; idx += kScanThreads) {
       const int tt = idx / dk, n = idx % dk;
       const float* row = proj + (int64_t)(t0 + tt) * ld;
-      const int at = tt * NP + n + (n / KMAX) * 4;
-      qs[at] = row[col_q + h * dk + n] * q_scale;
-      kk[at] = row[col_k + h * dk + n];
+      qs[idx] = row[col_q + h * dk + n] * q_scale;
+      kk[idx] = row[col_k + h * dk + n];
     }
     for (int idx = threadIdx.x; idx < nt * kCols; idx += kScanThreads) {
       const int tt = idx / kCols, c = idx % kCols;
@@ -195,21 +182,15 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
       m = m_new;
       const float tv = take * vs[tt * kCols + col];
       float num = 0.f, nq = 0.f;
-      const float4* k4 = reinterpret_cast<const float4*>(kk + tt * NP + ks * CH);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * NP + ks * CH);
 #pragma unroll
-      for (int i4 = 0; i4 < KMAX / 4; ++i4) {
-        const float4 kq = k4[i4], qq = q4[i4];
-        const float kvv[4] = {kq.x, kq.y, kq.z, kq.w}, qvv[4] = {qq.x, qq.y, qq.z, qq.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = i4 * 4 + e;
-          if (ks * KMAX + i < dk) {
-            S[i] = fmaf(keep, S[i], kvv[e] * tv);
-            nn[i] = fmaf(keep, nn[i], take * kvv[e]);
-            num = fmaf(S[i], qvv[e], num);
-            nq = fmaf(nn[i], qvv[e], nq);
-          }
+      for (int i = 0; i < KMAX; ++i) {
+        const int n = ks + kSplit * i;
+        if (n < dk) {
+          const float kv = kk[tt * dk + n], qv = qs[tt * dk + n];
+          S[i] = fmaf(keep, S[i], kv * tv);
+          nn[i] = fmaf(keep, nn[i], take * kv);
+          num = fmaf(S[i], qv, num);
+          nq = fmaf(nn[i], qv, nq);
         }
       }
       num = group8_sum(num);
@@ -225,7 +206,7 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < KMAX; ++i) {
-    const int n = ks * KMAX + i;
+    const int n = ks + kSplit * i;
     if (n < dk) {
       stage[n * (kCols + 1) + col] = S[i];
       if (blockIdx.z == 0 && col == 0) np[n] = nn[i];
@@ -325,7 +306,7 @@ template <typename TP, int KMAX>
 static int launch_ssm(const float* xbc, int64_t ld_xbc, int col_x, int col_B, int col_C, const float* dt_raw, int64_t ld_dt, int col_dt,
                       const void* dt_bias, const void* A_log, const void* Dskip, float* state, const int32_t* state_slots, const int32_t* cu_q,
                       const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int P, int N, int hpg, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * kChunk * kSplit * (KMAX + 4) + 2 * kChunk * kCols + 2 * kChunk + (size_t)N * (kCols + 1)) * 4;
+  const size_t smem = ((size_t)2 * kChunk * N + 2 * kChunk * kCols + 2 * kChunk + (size_t)N * (kCols + 1)) * 4;
   static bool cfg = false;
   if (!cfg) { cudaFuncSetAttribute(ssm_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); cfg = true; }
   dim3 grid((unsigned)B, (unsigned)H, (unsigned)((P + kCols - 1) / kCols));
@@ -356,7 +337,7 @@ template <typename TP, int KMAX>
 static int launch_mlstm(const float* proj, int64_t ld, int col_q, int col_k, int col_v, int col_i, int col_f, const void* i_bias, const void* f_bias,
                         float cap, float q_scale, float* S_state, float* n_state, float* m_state, const int32_t* state_slots, const int32_t* cu_q,
                         const int64_t* position_ids, float* y, int64_t ld_y, int B, int H, int dk, int dv, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * kChunk * kSplit * (KMAX + 4) + 2 * kChunk * kCols + 2 * kChunk + (size_t)dk * (kCols + 1)) * 4;
+  const size_t smem = ((size_t)2 * kChunk * dk + 2 * kChunk * kCols + 2 * kChunk + (size_t)dk * (kCols + 1)) * 4;
   static bool cfg = false;
   if (!cfg) { cudaFuncSetAttribute(mlstm_scan_kernel<TP, KMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); cfg = true; }
   dim3 grid((unsigned)B, (unsigned)H, (unsigned)((dv + kCols - 1) / kCols));
