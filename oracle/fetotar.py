@@ -1,9 +1,9 @@
 """Slow reference of the Fetotar decoder: plain PyTorch on the CPU, one function per mechanism, whole sequences at once.
 
-Checker only.  It shares no code with the product path (no paged cache, no state slots, no kernels): every mixer here
+Test infrastructure only.  It shares no code with the product path (no paged cache, no state slots, no kernels): every mixer here
 recomputes a sequence from its first token, so a test can compare any cut of a prompt, any batch and any reuse of pages and
 slots in the product against it.  `dtype` is torch.float64 by default: the product's 32-bit and bfloat16 results are both
-judged against the same numbers.
+compared with the same numbers.
 
 Checkpoint naming: `embed`, `side.embed`, `l<i>.norm1[.b]`, `l<i>.norm1b[.b]`, `l<i>.norm2[.b]`, `l<i>.norm2b[.b]`,
 `l<i>.mix.*`, `l<i>.mlp.{gate,up,down}`, `l<i>.side.{gate,proj,norm}`, `final.norm[.b]`, `head`.
