@@ -1,5 +1,6 @@
-/* C ABI of libb200_seq.so: kernels of the hybrid decoder families (latent attention over a paged latent cache, state-space
- * and matrix-memory mixers over fp32 state slots, row kernels around an fp32 residual stream).
+/* C ABI of libb200_seq.so: kernels of the decoder families with an fp32 residual stream (latent attention over a paged latent cache,
+ * multi-head attention with differential maps or a distance bias over paged heads, state-space and matrix-memory mixers over fp32
+ * state slots, routed feed-forward, row kernels around the stream).
  *
  * Conventions as in b200_tgis.h: plain device pointers + sizes + a cudaStream_t (void*), status-code return (0 = ok, the
  * message through b200_last_error()), no allocation, enqueue-only.  Element types are passed as codes: 0 = bfloat16,
@@ -68,6 +69,42 @@ int b200_seq_mlstm_scan(const float* proj, int64_t ld, int col_q, int col_k, int
                         const void* f_bias, int dt, float cap, float q_scale, float* S_state, float* n_state, float* m_state,
                         const int32_t* state_slots, const int32_t* cu_q, const int64_t* position_ids, float* y, int64_t ld_y, int B, int H,
                         int dk, int dv, void* stream);
+
+/* same convolution with the activation as a parameter: act 0 none, 1 SiLU; bias may be NULL */
+int b200_seq_causal_conv(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt, int act,
+                         float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
+                         const int64_t* position_ids, float* out, int64_t T, int B, void* stream);
+/* out[t] = table[ids[t]] + pos_table[position_ids[t]], fp32 */
+int b200_seq_embed_add_pos(const void* table, const void* pos_table, int dt, const int64_t* ids, const int64_t* position_ids, float* out,
+                           int64_t T, int64_t W, int64_t V, int64_t P, void* stream);
+/* out (type dt) = x / sqrt(mean x^2 + eps) * (w + w_offset) of fp32 rows */
+int b200_seq_rmsnorm_rows(const float* x, const void* w, int dt, float w_offset, void* out, int64_t T, int64_t W, float eps, void* stream);
+/* per token: unit-RMS (normalise != 0) of Hq query heads and Hk key heads of d elements, optional weights, queries times
+ * 1 + temp_coef ln(floor((p + 1) / temp_every) + 1); keys to cache[slot, k_off ..], Cv values to cache[slot, v_off ..], queries to
+ * q_out fp32 [T, Hq, d].  col_k / col_v < 0: the layer writes no keys / values */
+int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int d, const void* qnorm_w, float temp_coef, int temp_every,
+                           int col_k, int Hk, const void* knorm_w, int col_v, int Cv, int normalise, const int64_t* position_ids,
+                           const int64_t* slot_mapping, void* cache, int dt, int64_t row_width, int k_off, int v_off, float* q_out, int64_t T,
+                           float eps, void* stream);
+/* soft-max attention of H * maps query rows per token over G * maps paged key heads (d) and G value heads (dv) of its own sequence,
+ * causal, optional window, optional bias rel[bucket(distance), head] (fp32 [rel_rows, H]) after the scale; out fp32 [Tq, H * maps, dv] */
+int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
+                        int64_t bt_stride, const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int G,
+                        int maps, int d, int dv, int window, float scale, int page, const float* rel, const int32_t* bucket_tab,
+                        int n_bucket_tab, int rel_rows, void* stream);
+/* in fp32 [T, H, 2, dv] -> out [T, H * dv]: (a1 - lambda a2) / sqrt(mean(.^2) + eps) * out_scale */
+int b200_seq_diff_combine(const float* in, void* out, int out_dt, int64_t T, int H, int dv, float lambda, float out_scale, float eps,
+                          void* stream);
+/* routed feed-forward: top-k of fp32 router logits with soft-max weights over the picked logits, and the plan (compact rows expert by
+ * expert, tiles of 64 rows) that the grouped products and the combine read; plan = b200_seq_moe_plan_ints int32 values */
+int64_t b200_seq_moe_plan_ints(int64_t T, int E, int top);
+int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* ids, float* weights, int32_t* plan, void* stream);
+/* C[row] = W[expert(row)] A[gather ? token(row) : row] for the T * top rows of the plan; W [E, N, K] */
+int b200_seq_moe_linear(const void* A, int a_dt, int64_t lda, int gather, const void* W, int w_dt, void* C, int c_dt, int64_t ldc,
+                        int32_t* plan, int64_t T, int E, int top, int64_t N, int64_t K, void* stream);
+/* resid += mix + sum_k weights[t, k] y[row(t, k)]; mix and y may be NULL */
+int b200_seq_moe_combine_add(float* resid, const float* mix, const float* y, int64_t ldy, const float* weights, int32_t* plan, int64_t T,
+                             int E, int top, int64_t W, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,263 @@
+// Routed feed-forward (mixture of experts): every token picks the `top` experts with the largest router logits and weighs
+// them by the soft-max over the picked logits only.
+//
+//   moe_route_kernel   : one warp per token: top-k of the fp32 logits (ties: the lower expert), weights, and the token's place in
+//                        each picked expert's list (an atomic counter per expert; the order inside a list changes no result).
+//   moe_plan_kernel    : lists -> one compact row order (expert by expert) cut into tiles of 64 rows that never span two
+//                        experts; row <-> (token, pick) maps in both directions.
+//   moe_linear_kernel  : C[row] = W[expert of row's tile] A[row] over that plan; A rows are either the compact rows or gathered
+//                        through the row -> token map.  fp32 accumulation in ascending k: a row's result does not depend on what
+//                        else the step holds.
+//   moe_combine_add_kernel : resid[t] += mix[t] + sum over the token's picks, in pick order, of weight * y[row(t, pick)].
+//
+// Plan workspace (int32): [counts E][offsets E + 1][n_tiles 1][tile_expert max_tiles][tile_row0 max_tiles][place R][row_of R]
+// [token_of_row R] with R = T * top and max_tiles = ceil(R / 64) + E.
+#include "seq_common.cuh"
+
+namespace b200 {
+namespace seq {
+
+constexpr int kMoeTile = 64, kMoeStep = 16, kMaxTop = 8, kMaxExpertsPerLane = 8;
+
+struct MoePlan {
+  int32_t *counts, *offsets, *n_tiles, *tile_expert, *tile_row0, *place, *row_of, *token_of_row;
+  int64_t max_tiles;
+};
+
+__host__ __device__ inline int64_t moe_max_tiles(int64_t T, int E, int top) { return (T * top + kMoeTile - 1) / kMoeTile + E; }
+
+__host__ __device__ inline MoePlan moe_plan_view(int32_t* base, int64_t T, int E, int top) {
+  MoePlan p;
+  const int64_t R = T * top;
+  p.max_tiles = moe_max_tiles(T, E, top);
+  p.counts = base;
+  p.offsets = p.counts + E;
+  p.n_tiles = p.offsets + E + 1;
+  p.tile_expert = p.n_tiles + 1;
+  p.tile_row0 = p.tile_expert + p.max_tiles;
+  p.place = p.tile_row0 + p.max_tiles;
+  p.row_of = p.place + R;
+  p.token_of_row = p.row_of + R;
+  return p;
+}
+
+__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int64_t T, int E, int top, int32_t* __restrict__ ids,
+                                                        float* __restrict__ weights, int32_t* __restrict__ counts, int32_t* __restrict__ place) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = (int64_t)blockIdx.x * 8 + warp_id();
+  if (t >= T) return;
+  const int lane = lane_id();
+  float z[kMaxExpertsPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    z[i] = e < E ? logits[t * E + e] : -INFINITY;
+  }
+  float val[kMaxTop];
+  int idx[kMaxTop];
+#pragma unroll
+  for (int k = 0; k < kMaxTop; ++k) {
+    if (k >= top) break;
+    float best = -INFINITY;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && (z[i] > best || (z[i] == best && e < be))) { best = z[i]; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+    }
+    val[k] = best;
+    idx[k] = be;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+      if (lane + 32 * i == be) z[i] = -INFINITY;
+  }
+  if (lane == 0) {
+    float den = 0.f, w[kMaxTop];
+#pragma unroll
+    for (int k = 0; k < kMaxTop; ++k) {
+      if (k >= top) break;
+      w[k] = expf(val[k] - val[0]);  // val[0] is the largest
+      den += w[k];
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxTop; ++k) {
+      if (k >= top) break;
+      ids[t * top + k] = idx[k];
+      weights[t * top + k] = w[k] / den;
+      place[t * top + k] = atomicAdd(counts + idx[k], 1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_plan_kernel(const int32_t* __restrict__ ids, int64_t R, int top, int E, MoePlan p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      p.offsets[e] = off;
+      const int c = p.counts[e];
+      for (int r = 0; r < c; r += kMoeTile) {
+        p.tile_expert[nt] = e;
+        p.tile_row0[nt] = off + r;
+        ++nt;
+      }
+      off += c;
+    }
+    p.offsets[E] = off;
+    *p.n_tiles = nt;
+  }
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < R; i += blockDim.x) {
+    const int row = p.offsets[ids[i]] + p.place[i];
+    p.row_of[i] = row;
+    p.token_of_row[row] = (int32_t)(i / top);
+  }
+}
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) moe_linear_kernel(const TA* __restrict__ A, int64_t lda, int gather, const TW* __restrict__ W,
+                                                         TC* __restrict__ C, int64_t ldc, MoePlan p, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float As[kMoeStep][kMoeTile + 4];
+  __shared__ float Ws[kMoeStep][kMoeTile + 4];
+  __shared__ int64_t a_row[kMoeTile];
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;
+  const int e = p.tile_expert[tile], m0 = p.tile_row0[tile], m_end = p.offsets[e + 1];
+  W += (int64_t)e * N * K;
+  const int n0 = blockIdx.x * kMoeTile;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  if (tid < kMoeTile) {
+    const int m = m0 + tid;
+    a_row[tid] = m < m_end ? (gather ? (int64_t)p.token_of_row[m] : (int64_t)m) : -1;
+  }
+  __syncthreads();
+  float acc[4][4] = {};
+  const int64_t ar = a_row[lr];
+  for (int k0 = 0; k0 < K; k0 += kMoeStep) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      const int n = n0 + lr;
+      As[lk + i][lr] = (ar >= 0 && k < K) ? ldf(A + ar * lda + k) : 0.f;
+      Ws[lk + i][lr] = (n < N && k < K) ? ldf(W + (int64_t)n * K + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kMoeStep; ++k) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = As[k][ty * 4 + i];
+        w[i] = Ws[k][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= m_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) stf(C + (int64_t)m * ldc + n, acc[i][j]);
+    }
+  }
+}
+
+// top == 0 (or y == nullptr): resid += mix only
+__global__ void __launch_bounds__(256) moe_combine_add_kernel(float* __restrict__ resid, const float* __restrict__ mix, const float* __restrict__ y,
+                                                              int64_t ldy, const float* __restrict__ weights, const int32_t* __restrict__ row_of,
+                                                              int top, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += 256) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(weights[t * top + k], y[(int64_t)row_of[t * top + k] * ldy + i], acc);
+    resid[t * W + i] += (mix ? mix[t * W + i] : 0.f) + acc;
+  }
+}
+
+}  // namespace seq
+}  // namespace b200
+
+using namespace b200::seq;
+
+extern "C" int64_t b200_seq_moe_plan_ints(int64_t T, int E, int top) {
+  return (int64_t)E + E + 1 + 1 + 2 * moe_max_tiles(T, E, top) + 3 * T * top;
+}
+
+// logits fp32 [T, E] -> ids int32 [T, top], weights fp32 [T, top] and the plan (b200_seq_moe_plan_ints int32 values)
+extern "C" int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* ids, float* weights, int32_t* plan, void* stream) {
+  if (T == 0) return B200_OK;
+  if (E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 || top > kMaxTop || top > E) {
+    b200_set_last_error("seq_moe_route: need 1 <= top <= min(8, experts), experts <= 256");
+    return B200_ERR_ARG;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  MoePlan p = moe_plan_view(plan, T, E, top);
+  if (cudaMemsetAsync(p.counts, 0, sizeof(int32_t) * E, st) != cudaSuccess) { b200_set_last_error("seq_moe_route: memset failed"); return B200_ERR_CUDA; }
+  B200_LAUNCH(moe_route_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, st, logits, T, E, top, ids, weights, p.counts, p.place);
+  B200_LAUNCH(moe_plan_kernel, dim3(1), dim3(256), 0, st, (const int32_t*)ids, T * top, top, E, p);
+  b200_count_launches(2);
+  return B200_OK;
+}
+
+template <typename TA, typename TW, typename TC>
+static int launch_moe_linear(const void* A, int64_t lda, int gather, const void* W, void* C, int64_t ldc, MoePlan p, int64_t N, int64_t K,
+                             cudaStream_t st) {
+  dim3 grid((unsigned)((N + kMoeTile - 1) / kMoeTile), (unsigned)p.max_tiles);
+  B200_LAUNCH((moe_linear_kernel<TA, TW, TC>), grid, dim3(256), 0, st, (const TA*)A, lda, gather, (const TW*)W, (TC*)C, ldc, p, (int)N, (int)K);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// C[row, :N] = W[expert(row)] [N, K] . A[gather ? token(row) : row, :K] for the T * top compact rows of the plan; W [E, N, K] dense
+extern "C" int b200_seq_moe_linear(const void* A, int a_dt, int64_t lda, int gather, const void* W, int w_dt, void* C, int c_dt, int64_t ldc,
+                                   int32_t* plan, int64_t T, int E, int top, int64_t N, int64_t K, void* stream) {
+  if (T == 0 || N == 0) return B200_OK;
+  MoePlan p = moe_plan_view(plan, T, E, top);
+  if (p.max_tiles > 65535 || K <= 0) { b200_set_last_error("seq_moe_linear: bad sizes"); return B200_ERR_ARG; }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int key = a_dt * 4 + w_dt * 2 + c_dt;
+#define CASE(a, w, c, TA, TW, TC) \
+  case a * 4 + w * 2 + c: return launch_moe_linear<TA, TW, TC>(A, lda, gather, W, C, ldc, p, N, K, st)
+  switch (key) {
+    CASE(0, 0, 0, __nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    CASE(0, 0, 1, __nv_bfloat16, __nv_bfloat16, float);
+    CASE(1, 0, 1, float, __nv_bfloat16, float);
+    CASE(1, 1, 1, float, float, float);
+    default: break;
+  }
+#undef CASE
+  b200_set_last_error("seq_moe_linear: unsupported combination of element types");
+  return B200_ERR_UNSUPPORTED;
+}
+
+// resid fp32 [T, W] += mix (fp32 [T, W] or NULL) + sum_k weights[t, k] y[row_of(t, k)];  y NULL / top 0: the sum is empty
+extern "C" int b200_seq_moe_combine_add(float* resid, const float* mix, const float* y, int64_t ldy, const float* weights, int32_t* plan,
+                                        int64_t T, int E, int top, int64_t W, void* stream) {
+  if (T == 0) return B200_OK;
+  const int32_t* row_of = nullptr;
+  if (y != nullptr && top > 0) row_of = moe_plan_view(plan, T, E, top).row_of;
+  else top = 0;
+  B200_LAUNCH(moe_combine_add_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, resid, mix, y, ldy, weights, row_of, top, (int)W);
+  b200_count_launches(1);
+  return B200_OK;
+}

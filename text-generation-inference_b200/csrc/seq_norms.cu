@@ -1,4 +1,5 @@
-// Row kernels around an fp32 residual stream: scaled embedding lookup, layer norm in and out of the stream, RMS norm of a
+// Row kernels around an fp32 residual stream: embedding lookup (scaled, or plus a learned position row), layer norm in and out of
+// the stream, RMS norm of the stream with an offset weight, RMS norm of a
 // column slice, grouped RMS norm with a gate, the clamped gated feed-forward activation, and the per-layer token side input.
 // One block per token row; all statistics and the residual sum in fp32.
 #include "seq_common.cuh"
@@ -18,6 +19,38 @@ __global__ void __launch_bounds__(kRowThreads) embed_scale_kernel(const T* __res
   int64_t id = ids[t];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);
   for (int i = threadIdx.x; i < W; i += kRowThreads) out[t * W + i] = ldf(table + id * W + i) * scale;
+}
+
+// x[t, :] = table[id[t], :] + pos_table[position[t], :]  (learned absolute positions; fp32 residual stream)
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) embed_add_pos_kernel(const T* __restrict__ table, const T* __restrict__ pos_table,
+                                                                    const int64_t* __restrict__ ids, const int64_t* __restrict__ position_ids,
+                                                                    float* __restrict__ out, int W, int64_t V, int64_t P) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  int64_t id = ids[t], p = position_ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  p = p < 0 ? 0 : (p >= P ? P - 1 : p);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) out[t * W + i] = ldf(table + id * W + i) + ldf(pos_table + p * W + i);
+}
+
+// out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * (w + w_offset): RMS norm of the fp32 stream whose weight is stored around -w_offset
+// (w_offset 1: "one plus weight"; 0: plain weight)
+template <typename TP>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_rows_kernel(const float* __restrict__ x, const TP* __restrict__ w, float w_offset,
+                                                                   TP* __restrict__ out, int W, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const int64_t t = blockIdx.x;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float v = x[t * W + i];
+    q += v * v;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) stf(out + t * W + i, x[t * W + i] * rstd * (ldf(w + i) + w_offset));
 }
 
 // mode 0: out[t] = LN(x[t]) * w + b  (x fp32 or T, out T)      mode 1: resid[t] += LN(x[t]) * w + b  (resid fp32)
@@ -144,6 +177,24 @@ extern "C" int b200_seq_embed_scale(const void* table, int dt, const int64_t* id
   if (T == 0) return B200_OK;
   B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((embed_scale_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, (const E*)table, ids,
                                        scale, out, (int)W, V));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_embed_add_pos(const void* table, const void* pos_table, int dt, const int64_t* ids, const int64_t* position_ids,
+                                      float* out, int64_t T, int64_t W, int64_t V, int64_t P, void* stream) {
+  if (T == 0) return B200_OK;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((embed_add_pos_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, (const E*)table,
+                                       (const E*)pos_table, ids, position_ids, out, (int)W, V, P));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+extern "C" int b200_seq_rmsnorm_rows(const float* x, const void* w, int dt, float w_offset, void* out, int64_t T, int64_t W, float eps,
+                                     void* stream) {
+  if (T == 0) return B200_OK;
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((rmsnorm_rows_kernel<E>), dim3((unsigned)T), dim3(kRowThreads), 0, (cudaStream_t)stream, x, (const E*)w,
+                                       w_offset, (E*)out, (int)W, eps));
   b200_count_launches(1);
   return B200_OK;
 }

@@ -1,0 +1,273 @@
+// Multi-head attention over paged per-head keys and values, for decoders whose layers cache one row per token:
+//   cache row = [ ... keys of every key head (k_off) ... | ... values of every value head (v_off) ... ]   (any widths, one element type)
+//
+//   heads_prepare_kernel : from a token's projected (and, where the layer has one, convolved) row: RMS-norms every query head and
+//                          key head over its `d` elements (optional weight), multiplies the queries by the position's temperature
+//                          1 + coef * ln(floor((p + 1) / every) + 1), writes keys and values into the token's cache slot and the
+//                          queries into a dense fp32 buffer.  A layer that reads another layer's cache passes no key / value columns.
+//   paged_heads_attn_kernel : one block per (query token, key/value head): the query rows that share that head - `rep` query heads
+//                          times `maps` soft-max maps (differential attention keeps two keys per head and one value) - each take a
+//                          warp; key tiles of 32 rows pass through shared memory, fp32 online soft-max.  Optional learned bias per
+//                          (distance bucket, head), added after the scale; optional sliding window.  Prompts, portions of prompts
+//                          and decoded tokens are the same case: every key is read back from the cache.
+//   diff_combine_kernel  : o = a1 - lambda a2 per head, o / sqrt(mean(o^2) + eps) * out_scale.
+#include "seq_common.cuh"
+
+#include <cstdlib>
+
+namespace b200 {
+namespace seq {
+
+constexpr int kPrepThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepThreads) heads_prepare_kernel(
+    const float* __restrict__ src, int64_t ld, int col_q, int Hq, int d, const T* __restrict__ qnorm_w, float temp_coef, int temp_every,
+    int col_k, int Hk, const T* __restrict__ knorm_w, int col_v, int Cv, int normalise, const int64_t* __restrict__ position_ids,
+    const int64_t* __restrict__ slot_mapping, T* __restrict__ cache, int64_t RW, int k_off, int v_off, float* __restrict__ q_out, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int w = warp_id(), lane = lane_id(), nw = kPrepThreads / 32;
+  const int64_t pos = position_ids[t];
+  const int64_t slot = slot_mapping[t];
+  const float* row = src + t * ld;
+  float temp = 1.f;
+  if (temp_coef != 0.f && temp_every > 0) temp = 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f);
+  const int n_heads = Hq + (col_k >= 0 ? Hk : 0);
+  for (int hh = w; hh < n_heads; hh += nw) {
+    const bool is_q = hh < Hq;
+    const int h = is_q ? hh : hh - Hq;
+    const float* v = row + (is_q ? col_q : col_k) + (int64_t)h * d;
+    float rstd = 1.f;
+    if (normalise) {
+      float s = 0.f;
+      for (int i = lane; i < d; i += 32) s += v[i] * v[i];
+      rstd = 1.f / sqrtf(warp_sum(s) / d + eps);
+    }
+    const T* nw_ptr = is_q ? qnorm_w : knorm_w;
+    if (is_q) {
+      float* dst = q_out + (t * Hq + h) * d;
+      for (int i = lane; i < d; i += 32) dst[i] = v[i] * rstd * (nw_ptr ? ldf(nw_ptr + i) : 1.f) * temp;
+    } else if (slot >= 0) {
+      T* dst = cache + slot * RW + k_off + (int64_t)h * d;
+      for (int i = lane; i < d; i += 32) stf(dst + i, v[i] * rstd * (nw_ptr ? ldf(nw_ptr + i) : 1.f));
+    }
+  }
+  if (col_v >= 0 && slot >= 0) {
+    T* dst = cache + slot * RW + v_off;
+    for (int i = threadIdx.x; i < Cv; i += kPrepThreads) stf(dst + i, row[col_v + i]);
+  }
+}
+
+constexpr int kAttnWarps = 8, kKeyTile = 32;
+
+// RPW query rows per warp, NV = ceil(dv / 32) value columns per lane
+template <typename T, int RPW, int NV>
+__global__ void __launch_bounds__(kAttnWarps * 32) paged_heads_attn_kernel(
+    const float* __restrict__ q, const T* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
+    int64_t bt_stride, const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H,
+    int rep, int maps, int d, int dv, int window, float scale, int page, const float* __restrict__ rel, const int32_t* __restrict__ bucket_tab,
+    int n_bucket_tab, int rel_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int KD = maps * d, KP = KD + 1, rows_g = rep * maps, rows_blk = kAttnWarps * RPW;
+  float* qs = sm;                       // [rows_blk][d]
+  float* ks = qs + rows_blk * d;        // [kKeyTile][KP]
+  float* vs = ks + kKeyTile * KP;       // [kKeyTile][dv]
+  const int64_t t = blockIdx.x;
+  const int g = blockIdx.y, r_base = blockIdx.z * rows_blk;
+  const int w = warp_id(), lane = lane_id();
+  const int Hq = H * maps;
+  const int b = seq_of_token[t];
+  const int p = (int)position_ids[t];
+  const int j_lo = max(0, p - window + 1);
+  const int nthreads = kAttnWarps * 32;
+  // row r of the group: query head g * rep + r / maps, map r % maps
+  for (int idx = threadIdx.x; idx < rows_blk * d; idx += nthreads) {
+    const int r = r_base + idx / d;
+    float v = 0.f;
+    if (r < rows_g) {
+      const int qh = (g * rep + r / maps) * maps + r % maps;
+      v = q[(t * Hq + qh) * d + idx % d];
+    }
+    qs[idx] = v;
+  }
+  float m[RPW], l[RPW], acc[RPW][NV];
+#pragma unroll
+  for (int a = 0; a < RPW; ++a) {
+    m[a] = -INFINITY;
+    l[a] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) acc[a][i] = 0.f;
+  }
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  for (int j0 = j_lo; j0 <= p; j0 += kKeyTile) {
+    __syncthreads();
+    const int nk = min(kKeyTile, p - j0 + 1);
+    for (int idx = threadIdx.x; idx < nk * KD; idx += nthreads) {
+      const int jj = idx / KD, dd = idx % KD;
+      const int j = j0 + jj;
+      const int64_t row = (int64_t)table[j / page] * page + j % page;
+      ks[jj * KP + dd] = ldf(cache + row * RW + k_off + (int64_t)g * KD + dd);
+    }
+    for (int idx = threadIdx.x; idx < nk * dv; idx += nthreads) {
+      const int jj = idx / dv, dd = idx % dv;
+      const int j = j0 + jj;
+      const int64_t row = (int64_t)table[j / page] * page + j % page;
+      vs[jj * dv + dd] = ldf(cache + row * RW + v_off + (int64_t)g * dv + dd);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < RPW; ++a) {
+      const int rl = w * RPW + a, r = r_base + rl;
+      if (r >= rows_g) continue;  // warp-uniform
+      const int mp = r % maps, h = g * rep + r / maps;
+      float s = -INFINITY;
+      if (lane < nk) {
+        float dot = 0.f;
+        const float* kq = ks + lane * KP + mp * d;
+        const float* qq = qs + rl * d;
+        for (int i = 0; i < d; ++i) dot = fmaf(qq[i], kq[i], dot);
+        s = dot * scale;
+        if (rel) {
+          const int dist = p - (j0 + lane);
+          const int bk = dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1;
+          s += rel[bk * H + h];
+        }
+      }
+      const float m_new = fmaxf(m[a], warp_max(s));
+      const float pr = lane < nk ? expf(s - m_new) : 0.f;
+      const float corr = expf(m[a] - m_new);
+      l[a] = l[a] * corr + warp_sum(pr);
+      m[a] = m_new;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) acc[a][i] *= corr;
+      for (int jj = 0; jj < nk; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pr, jj);
+        const float* vr = vs + jj * dv;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int c = lane + 32 * i;
+          if (c < dv) acc[a][i] = fmaf(pj, vr[c], acc[a][i]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < RPW; ++a) {
+    const int r = r_base + w * RPW + a;
+    if (r >= rows_g) continue;
+    const int qh = (g * rep + r / maps) * maps + r % maps;
+    const float inv = 1.f / l[a];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < dv) out[(t * Hq + qh) * dv + c] = acc[a][i] * inv;
+    }
+  }
+}
+
+// in [T, H, 2, dv] fp32 (two maps per head) -> out [T, H * dv]: o = a1 - lambda a2, unit RMS over dv, times out_scale
+template <typename TO>
+__global__ void __launch_bounds__(256) diff_combine_kernel(const float* __restrict__ in, TO* __restrict__ out, int H, int dv, float lambda,
+                                                           float out_scale, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int lane = lane_id();
+  for (int h = warp_id(); h < H; h += 8) {
+    const float* a1 = in + ((t * H + h) * 2) * dv;
+    const float* a2 = a1 + dv;
+    float s = 0.f;
+    for (int i = lane; i < dv; i += 32) {
+      const float o = a1[i] - lambda * a2[i];
+      s += o * o;
+    }
+    const float rstd = 1.f / sqrtf(warp_sum(s) / dv + eps);
+    for (int i = lane; i < dv; i += 32) stf(out + (t * H + h) * dv + i, (a1[i] - lambda * a2[i]) * rstd * out_scale);
+  }
+}
+
+}  // namespace seq
+}  // namespace b200
+
+using namespace b200::seq;
+
+// src: fp32 rows (leading dimension ld) holding Hq query heads of d elements from col_q, Hk key heads from col_k (col_k < 0: the
+// layer writes no keys), Cv value elements from col_v (col_v < 0: no values).  normalise != 0: unit RMS over d per head (eps), times
+// the weight when given.  Queries are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) (temp_coef 0: by 1).
+extern "C" int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int d, const void* qnorm_w, float temp_coef,
+                                      int temp_every, int col_k, int Hk, const void* knorm_w, int col_v, int Cv, int normalise,
+                                      const int64_t* position_ids, const int64_t* slot_mapping, void* cache, int dt, int64_t row_width,
+                                      int k_off, int v_off, float* q_out, int64_t T, float eps, void* stream) {
+  if (T == 0) return B200_OK;
+  if (Hq <= 0 || d <= 0) { b200_set_last_error("seq_heads_prepare: bad sizes"); return B200_ERR_ARG; }
+  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((heads_prepare_kernel<E>), dim3((unsigned)T), dim3(kPrepThreads), 0, (cudaStream_t)stream, src, ld, col_q, Hq,
+                                       d, (const E*)qnorm_w, temp_coef, temp_every, col_k, Hk, (const E*)knorm_w, col_v, Cv, normalise,
+                                       position_ids, slot_mapping, (E*)cache, row_width, k_off, v_off, q_out, eps));
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+template <typename T, int RPW, int NV>
+static int launch_paged_heads_attn(const float* q, const void* cache, int64_t RW, int k_off, int v_off, const int32_t* block_table,
+                                   int64_t bt_stride, const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H,
+                                   int G, int maps, int d, int dv, int window, float scale, int page, const float* rel,
+                                   const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, cudaStream_t st) {
+  const int rep = H / G, rows_g = rep * maps, rows_blk = kAttnWarps * RPW;
+  const size_t smem = ((size_t)rows_blk * d + (size_t)kKeyTile * (maps * d + 1) + (size_t)kKeyTile * dv) * 4;
+  if (smem > 200 * 1024) { b200_set_last_error("seq_paged_attn: heads too wide"); return B200_ERR_ARG; }
+  static bool cfg = false;
+  if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_kernel<T, RPW, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; }
+  dim3 grid((unsigned)Tq, (unsigned)G, (unsigned)((rows_g + rows_blk - 1) / rows_blk));
+  B200_LAUNCH((paged_heads_attn_kernel<T, RPW, NV>), grid, dim3(kAttnWarps * 32), smem, st, q, (const T*)cache, RW, k_off, v_off, block_table,
+              bt_stride, seq_of_token, position_ids, out, H, rep, maps, d, dv, window, scale, page, rel, bucket_tab, n_bucket_tab, rel_rows);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// q fp32 [Tq, H * maps, d] (query head h, map m at index h * maps + m); cache [blocks, page, row_width] of type dt with G * maps key
+// heads of d elements from k_off (key head g, map m at g * maps + m) and G value heads of dv elements from v_off; out fp32
+// [Tq, H * maps, dv].  window <= 0: every earlier token is visible.  rel (fp32 [rel_rows, H]) NULL: no bias; otherwise
+// rel[bucket(distance), h] is added to the scaled score, bucket(n) = bucket_tab[n] for n < n_bucket_tab and rel_rows - 1 beyond.
+extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off,
+                                   const int32_t* block_table, int64_t bt_stride, const int32_t* seq_of_token, const int64_t* position_ids,
+                                   float* out, int64_t Tq, int H, int G, int maps, int d, int dv, int window, float scale, int page,
+                                   const float* rel, const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, void* stream) {
+  if (Tq == 0) return B200_OK;
+  if (G <= 0 || H % G != 0 || maps < 1 || d <= 0 || dv <= 0 || dv > 512) {
+    b200_set_last_error("seq_paged_attn: need heads % kv_heads == 0, maps >= 1, 0 < vdim <= 512");
+    return B200_ERR_ARG;
+  }
+  if (window <= 0) window = 0x3fffffff;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rows_g = (H / G) * maps;
+  const int nv = (dv + 31) / 32;
+#define PA(RPW, NV)                                                                                                                      \
+  B200_SEQ_DISPATCH(dt, E, return (launch_paged_heads_attn<E, RPW, NV>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, \
+                                                                       position_ids, out, Tq, H, G, maps, d, dv, window, scale, page, rel,  \
+                                                                       bucket_tab, n_bucket_tab, rel_rows, st)))
+#define PA_NV(RPW)            \
+  do {                        \
+    if (nv <= 2) PA(RPW, 2);  \
+    else if (nv <= 4) PA(RPW, 4); \
+    else if (nv <= 8) PA(RPW, 8); \
+    else PA(RPW, 16);         \
+  } while (0)
+  if (rows_g <= kAttnWarps) PA_NV(1);
+  else PA_NV(2);
+#undef PA_NV
+#undef PA
+  return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200_seq_diff_combine(const float* in, void* out, int out_dt, int64_t T, int H, int dv, float lambda, float out_scale, float eps,
+                                     void* stream) {
+  if (T == 0) return B200_OK;
+  B200_SEQ_DISPATCH(out_dt, E, B200_LAUNCH((diff_combine_kernel<E>), dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, in, (E*)out, H, dv, lambda,
+                                           out_scale, eps));
+  b200_count_launches(1);
+  return B200_OK;
+}

@@ -224,7 +224,7 @@ constexpr int kMaxTaps = 8;
 
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in(p - (taps-1) + j)), p the token's position; inputs before this step's first token
 // come from the sequence's conv state (positions >= 0) or are zero (before the sequence starts)
-template <typename TP>
+template <typename TP, int ACT>  // ACT 0: no activation, 1: SiLU
 __global__ void causal_conv_silu_kernel(const float* __restrict__ u, int64_t ld_u, int col0, int C, int taps, const TP* __restrict__ w,
                                         const TP* __restrict__ bias, const float* __restrict__ conv_state, const int32_t* __restrict__ state_slots,
                                         const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ cu_q,
@@ -238,7 +238,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ u, int64_t ld_
   const int row0 = cu_q[b];
   const int64_t s = position_ids[row0], p = position_ids[t];
   const float* st = conv_state + (int64_t)state_slots[b] * (taps - 1) * C;
-  float acc = ldf(bias + c);
+  float acc = bias ? ldf(bias + c) : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int64_t pp = p - (taps - 1) + j;
     float val = 0.f;
@@ -246,7 +246,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ u, int64_t ld_
     else if (pp >= 0) val = st[(pp - s + taps - 1) * C + c];
     acc = fmaf(ldf(w + (int64_t)c * taps + j), val, acc);
   }
-  out[t * C + c] = silu_f(acc);
+  out[t * C + c] = ACT == 1 ? silu_f(acc) : acc;
 }
 
 // after the convolution: the state becomes the last taps-1 inputs of the sequence (older state entries shift when the step
@@ -287,19 +287,30 @@ __global__ void conv_state_update_kernel(const float* __restrict__ u, int64_t ld
 
 using namespace b200::seq;
 
-extern "C" int b200_seq_causal_conv_silu(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt,
-                                         float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
-                                         const int64_t* position_ids, float* out, int64_t T, int B, void* stream) {
+// act 0: out = convolution (+ bias when given); act 1: SiLU of that
+extern "C" int b200_seq_causal_conv(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt, int act,
+                                    float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
+                                    const int64_t* position_ids, float* out, int64_t T, int B, void* stream) {
   if (T == 0) return B200_OK;
-  if (taps < 1 || taps > kMaxTaps) { b200_set_last_error("seq_causal_conv_silu: 1 <= taps <= 8"); return B200_ERR_ARG; }
+  if (taps < 1 || taps > kMaxTaps) { b200_set_last_error("seq_causal_conv: 1 <= taps <= 8"); return B200_ERR_ARG; }
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned cb = (unsigned)((C + 255) / 256);
-  B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((causal_conv_silu_kernel<E>), dim3((unsigned)T, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, (const E*)w,
-                                       (const E*)bias, (const float*)conv_state, state_slots, seq_of_token, cu_q, position_ids, out));
+  if (act == 1)
+    B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((causal_conv_silu_kernel<E, 1>), dim3((unsigned)T, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, (const E*)w,
+                                         (const E*)bias, (const float*)conv_state, state_slots, seq_of_token, cu_q, position_ids, out));
+  else
+    B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((causal_conv_silu_kernel<E, 0>), dim3((unsigned)T, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, (const E*)w,
+                                         (const E*)bias, (const float*)conv_state, state_slots, seq_of_token, cu_q, position_ids, out));
   if (taps > 1)
     B200_LAUNCH(conv_state_update_kernel, dim3((unsigned)B, cb), dim3(256), 0, st, u, ld_u, col0, C, taps, conv_state, state_slots, cu_q, position_ids);
   b200_count_launches(2);
   return B200_OK;
+}
+
+extern "C" int b200_seq_causal_conv_silu(const float* u, int64_t ld_u, int col0, int C, int taps, const void* w, const void* bias, int dt,
+                                         float* conv_state, const int32_t* state_slots, const int32_t* seq_of_token, const int32_t* cu_q,
+                                         const int64_t* position_ids, float* out, int64_t T, int B, void* stream) {
+  return b200_seq_causal_conv(u, ld_u, col0, C, taps, w, bias, dt, 1, conv_state, state_slots, seq_of_token, cu_q, position_ids, out, T, B, stream);
 }
 
 template <typename TP, int KMAX>

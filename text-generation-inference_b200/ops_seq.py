@@ -1,5 +1,6 @@
-"""Tensor-level wrappers over libb200_seq.so: the kernels of the hybrid decoder families (latent attention over a paged latent
-cache, state-space and matrix-memory mixers over fp32 state slots, the row kernels around an fp32 residual stream).
+"""Tensor-level wrappers over libb200_seq.so: the kernels of the decoder families with an fp32 stream (latent attention over a paged latent
+cache, differential and distance-biased attention over paged heads, state-space and matrix-memory mixers over fp32 state slots,
+routed feed-forward, the row kernels around the residual stream).
 
 Element type `dtype` is torch.bfloat16 or torch.float32 (weights, activations between projections, cache pages); statistics,
 soft-max, recurrences, states and the residual stream are fp32 in both.  CUDA tensors only; there is no eager fallback.
@@ -252,3 +253,131 @@ def mlstm_scan(proj: torch.Tensor, col_q: int, col_k: int, col_v: int, col_i: in
         _ptr(S), _ptr(n), _ptr(m), _ptr(step.state_slots), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(y), y.stride(0), step.B, H, dk, dv,
         _stream()), "seq_mlstm_scan")
     return y
+
+
+def causal_conv(u: torch.Tensor, col0: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor], conv_state: torch.Tensor,
+                step: RaggedStep, act_silu: bool = False) -> torch.Tensor:
+    """Depth-wise causal convolution (optionally + bias, optionally SiLU) of the columns [col0, col0 + channels) of u (fp32); state as
+    in causal_conv_silu."""
+    _cuda(u, w, bias, conv_state)
+    assert u.dtype == torch.float32 and conv_state.dtype == torch.float32 and w.is_contiguous() and conv_state.is_contiguous()
+    out = torch.empty(step.T, channels, dtype=torch.float32, device=u.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_causal_conv(
+        _ptr(u), u.stride(0), col0, channels, w.shape[1], _ptr(w), _ptr(bias), _dt(w), int(act_silu), _ptr(conv_state), _ptr(step.state_slots),
+        _ptr(step.seq_of_token), _ptr(step.cu_q), _ptr(step.position_ids), _ptr(out), step.T, step.B, _stream()), "seq_causal_conv")
+    return out
+
+
+def embed_add_pos(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, position_ids: torch.Tensor) -> torch.Tensor:
+    """-> fp32 [T, W] = table[ids] + pos_table[position_ids] (learned absolute positions)."""
+    _cuda(table, pos_table, ids, position_ids)
+    assert ids.dtype == torch.int64 and position_ids.dtype == torch.int64 and table.is_contiguous() and pos_table.is_contiguous()
+    assert table.dtype == pos_table.dtype and table.shape[1] == pos_table.shape[1]
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_embed_add_pos(_ptr(table), _ptr(pos_table), _dt(table), _ptr(ids), _ptr(position_ids), _ptr(out),
+                                                          ids.shape[0], table.shape[1], table.shape[0], pos_table.shape[0], _stream()),
+                   "seq_embed_add_pos")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, w_offset: float = 0.0) -> torch.Tensor:
+    """x fp32 [T, W] -> x / sqrt(mean(x^2) + eps) * (w + w_offset) in w's element type."""
+    _cuda(x, w)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    out = torch.empty(x.shape, dtype=w.dtype, device=x.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_rmsnorm_rows(_ptr(x), _ptr(w), _dt(w), float(w_offset), _ptr(out), x.shape[0], x.shape[1], float(eps),
+                                                         _stream()), "seq_rmsnorm_rows")
+    return out
+
+
+def heads_prepare(src: torch.Tensor, *, col_q: int, q_heads: int, dim: int, q_norm_w: Optional[torch.Tensor], temp_coef: float, temp_every: int,
+                  col_k: int, k_heads: int, k_norm_w: Optional[torch.Tensor], col_v: int, v_width: int, normalise: bool, step: RaggedStep,
+                  cache: torch.Tensor, k_off: int, v_off: int, eps: float) -> torch.Tensor:
+    """src fp32 [T, C]: unit-RMS per head (optional weight) of the query heads at col_q and the key heads at col_k, the queries times
+    the position's temperature; keys -> cache[slot, k_off:], v_width values from col_v -> cache[slot, v_off:]; -> queries fp32
+    [T, q_heads, dim].  col_k / col_v < 0: the layer writes no keys / values (it reads another layer's rows)."""
+    _cuda(src, cache, q_norm_w, k_norm_w)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and cache.is_contiguous()
+    q = torch.empty(step.T, q_heads, dim, dtype=torch.float32, device=src.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_heads_prepare(
+        _ptr(src), src.stride(0), col_q, q_heads, dim, _ptr(q_norm_w), float(temp_coef), int(temp_every), col_k, k_heads, _ptr(k_norm_w), col_v,
+        v_width, int(normalise), _ptr(step.position_ids), _ptr(step.slot_mapping), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off,
+        _ptr(q), step.T, float(eps), _stream()), "seq_heads_prepare")
+    return q
+
+
+def paged_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, heads: int, kv_heads: int, maps: int, vdim: int, k_off: int,
+               v_off: int, scale: float, window: int = 0, rel: Optional[torch.Tensor] = None, bucket_tab: Optional[torch.Tensor] = None
+               ) -> torch.Tensor:
+    """q fp32 [T, heads * maps, dim]; cache [blocks, page, row] with kv_heads * maps key heads at k_off and kv_heads value heads (vdim)
+    at v_off -> fp32 [T, heads * maps, vdim]: causal soft-max attention of every token over its own sequence's cache rows.
+    rel fp32 [rows, heads] + bucket_tab int32 [n]: rel[bucket(i - j), head] is added to the scaled score, bucket(n) = bucket_tab[n]
+    below len(bucket_tab), rows - 1 from there on."""
+    _cuda(q, cache, rel, bucket_tab)
+    T, Hq, d = q.shape
+    assert Hq == heads * maps and q.is_contiguous() and cache.is_contiguous() and q.dtype == torch.float32
+    assert rel is None or (rel.dtype == torch.float32 and rel.is_contiguous() and rel.shape[1] == heads and bucket_tab.dtype == torch.int32)
+    out = torch.empty(T, Hq, vdim, dtype=torch.float32, device=q.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_paged_attn(
+        _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
+        _ptr(step.seq_of_token), _ptr(step.position_ids), _ptr(out), T, heads, kv_heads, maps, d, vdim, int(window), float(scale),
+        cache.shape[1], _ptr(rel), _ptr(bucket_tab), 0 if bucket_tab is None else bucket_tab.shape[0], 0 if rel is None else rel.shape[0],
+        _stream()), "seq_paged_attn")
+    return out
+
+
+def diff_combine(maps_out: torch.Tensor, heads: int, vdim: int, lam: float, out_scale: float, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """maps_out fp32 [T, heads * 2, vdim] -> [T, heads * vdim]: (a1 - lam a2) / sqrt(mean(.^2) + eps) * out_scale per head."""
+    _cuda(maps_out)
+    assert maps_out.dtype == torch.float32 and maps_out.is_contiguous() and maps_out.shape[1:] == (heads * 2, vdim)
+    T = maps_out.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=out_dtype, device=maps_out.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_diff_combine(_ptr(maps_out), _ptr(out), _dt(out), T, heads, vdim, float(lam), float(out_scale),
+                                                         float(eps), _stream()), "seq_diff_combine")
+    return out
+
+
+@dataclass
+class MoeRouting:
+    """picks of a step's tokens and the compact row plan the grouped products read"""
+    T: int
+    experts: int
+    top: int
+    ids: torch.Tensor       # [T, top] int32
+    weights: torch.Tensor   # [T, top] fp32
+    plan: torch.Tensor      # int32 workspace (b200_seq_moe_plan_ints)
+
+
+def moe_route(logits: torch.Tensor, top: int) -> MoeRouting:
+    """logits fp32 [T, E] -> the `top` largest per token (ties: the lower expert), weights = soft-max over the picked logits."""
+    _cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    T, E = logits.shape
+    lib = _lib.load_seq()
+    ids = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    plan = torch.empty(int(lib.b200_seq_moe_plan_ints(T, E, top)), dtype=torch.int32, device=logits.device)
+    _lib.check_seq(lib.b200_seq_moe_route(_ptr(logits), T, E, top, _ptr(ids), _ptr(weights), _ptr(plan), _stream()), "seq_moe_route")
+    return MoeRouting(T, E, top, ids, weights, plan)
+
+
+def moe_linear(a: torch.Tensor, w: torch.Tensor, r: MoeRouting, gather: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """w [E, N, K]; a [T, K] (gather: the row of each pick's token) or [T * top, K] (compact rows) -> [T * top, N] compact rows."""
+    _cuda(a, w)
+    E, N, K = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and E == r.experts and a.shape[0] == (r.T if gather else r.T * r.top)
+    out = torch.empty(r.T * r.top, N, dtype=out_dtype, device=a.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_moe_linear(_ptr(a), _dt(a), a.stride(0), int(gather), _ptr(w), _dt(w), _ptr(out), _dt(out),
+                                                       out.stride(0), _ptr(r.plan), r.T, E, r.top, N, K, _stream()), "seq_moe_linear")
+    return out
+
+
+def moe_combine_add(resid: torch.Tensor, mix: Optional[torch.Tensor], y: Optional[torch.Tensor], r: Optional[MoeRouting]) -> None:
+    """resid (fp32, in place) += mix + sum_k weights[t, k] y[row(t, k)]; either addend may be None."""
+    _cuda(resid, mix, y)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and (mix is None or (mix.dtype == torch.float32 and mix.is_contiguous()))
+    assert y is None or (y.dtype == torch.float32 and y.stride(1) == 1 and r is not None)
+    T, W = resid.shape
+    _lib.check_seq(_lib.load_seq().b200_seq_moe_combine_add(
+        _ptr(resid), _ptr(mix), _ptr(y), 0 if y is None else y.stride(0), None if y is None else _ptr(r.weights), None if y is None else _ptr(r.plan),
+        T, 0 if y is None else r.experts, 0 if y is None else r.top, W, _stream()), "seq_moe_combine_add")

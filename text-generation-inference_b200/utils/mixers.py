@@ -1,6 +1,8 @@
 """Sequence mixers beyond plain multi-head attention, each with its constants as constructor arguments so that any decoder
 family can compose them: latent attention over a paged latent cache (sliding window, rotary part with optional YaRN frequency
-scaling), the selective state-space mixer (Mamba-2 form) and the matrix-memory mixer (mLSTM).
+scaling), the selective state-space mixer (Mamba-2 form), the matrix-memory mixer (mLSTM), differential attention (two soft-max
+maps per head, short convolutions after the projections, optionally over another layer's keys and values), attention with a
+learned bias per log-spaced distance bucket, and the feed-forward layers (clamped gated MLP, routed experts).
 
 A mixer declares what it keeps per sequence (`cache_spec`): a row of the paged cache per token, or fp32 state tensors in a
 state slot.  `forward(h, step, store)` takes the normed hidden states of a ragged step (ops_seq.RaggedStep: any mix of whole
@@ -11,7 +13,7 @@ the recurrences and the states are fp32 whatever the element type.
 from __future__ import annotations
 
 import math
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 from torch import nn
@@ -180,3 +182,135 @@ class ClampedGatedMLP(nn.Module):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.linear(ops.ff_clamped_gate(ops.linear(h, self.w_gate_up), self.limit, self.alpha), self.w_down)
+
+
+def log_distance_buckets(rows: int, far: float) -> List[int]:
+    """bucket of every distance up to the first one that reaches the last row: distances below rows // 2 have a row each, from there
+    rows are spaced evenly in ln(distance) up to `far`; every larger distance takes the last row"""
+    half = rows // 2
+    if half < 1 or far <= half:
+        raise ValueError("distance buckets need at least two rows and a far distance beyond rows / 2")
+    out, n = [], 0
+    while True:
+        b = n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b >= rows - 1:
+            return out
+        n += 1
+
+
+class DifferentialAttention(nn.Module):
+    """Grouped-query attention with two soft-max maps per head over the same values: o = a1 - lambda a2, unit-RMS per head, times
+    (1 - diff); lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff.  Queries and keys hold [map 1 | map 2] per head.  A depth-wise
+    causal convolution (`conv` taps, no bias) follows each of the q / k / v projections; queries and keys are then RMS-normed per
+    head and map with a weight shared by all heads, and queries are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1).
+    No rotation.  Per sequence: a cache row [keys after convolution and norm | values after convolution] per token and the last
+    conv - 1 projected rows (fp32 state slot).  `own_kv` False: the layer has no key / value tensors and reads the rows of another
+    layer with the same head counts (its `forward` is given that layer's pool).
+    Tensors under `prefix`: q, q.conv, q.norm, [k, k.conv, k.norm, v, v.conv,] lq1, lk1, lq2, lk2, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, vdim: int, conv: int, scale: float, diff: float,
+                 temp_coef: float, temp_every: int, eps: float, own_kv: bool = True, window: Optional[int] = None):
+        super().__init__()
+        _need_single_rank(weights, "DifferentialAttention")
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.d, self.dv, self.taps = heads, kv_heads, dim, vdim, int(conv)
+        self.scale, self.diff, self.eps, self.own_kv, self.window = float(scale), float(diff), float(eps), bool(own_kv), int(window or 0)
+        self.temp_coef, self.temp_every = float(temp_coef), int(temp_every)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        names = ["q", "k", "v"] if own_kv else ["q"]
+        self.w_in = torch.cat([get(n) for n in names], 0).contiguous()                   # -> [q | k | v]
+        self.conv_w = torch.cat([get(f"{n}.conv") for n in names], 0).contiguous()
+        self.q_norm = get("q.norm").contiguous()
+        self.k_norm = get("k.norm").contiguous() if own_kv else None
+        lam = [(get(a).float() * get(b).float()).sum() for a, b in (("lq1", "lk1"), ("lq2", "lk2"))]
+        self.lam = float(torch.exp(lam[0]) - torch.exp(lam[1])) + self.diff
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+        self.cq, self.ck, self.cv = heads * 2 * dim, kv_heads * 2 * dim, kv_heads * vdim
+        self.channels = self.cq + (self.ck + self.cv if own_kv else 0)
+        if self.w_in.shape[0] != self.channels or self.conv_w.shape != (self.channels, self.taps):
+            raise ValueError(f"{prefix}: projection / convolution shapes do not match the head sizes")
+
+    def cache_spec(self) -> LayerCacheSpec:
+        state = {"conv": (max(self.taps - 1, 1), self.channels)}
+        return LayerCacheSpec(kind="paged", row_width=self.ck + self.cv, state=state) if self.own_kv else LayerCacheSpec(kind="state", state=state)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages: torch.Tensor, state: Dict[str, torch.Tensor], max_s: int) -> torch.Tensor:
+        """`pages`: this layer's pool, or the pool of the layer whose keys and values it reads -> fp32 [T, width]"""
+        u = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        c = ops.causal_conv(u, 0, self.channels, self.conv_w, None, state["conv"], step)
+        own = self.own_kv
+        q = ops.heads_prepare(c, col_q=0, q_heads=self.H * 2, dim=self.d, q_norm_w=self.q_norm, temp_coef=self.temp_coef,
+                              temp_every=self.temp_every, col_k=self.cq if own else -1, k_heads=self.G * 2, k_norm_w=self.k_norm,
+                              col_v=self.cq + self.ck if own else -1, v_width=self.cv, normalise=True, step=step, cache=pages, k_off=0,
+                              v_off=self.ck, eps=self.eps)
+        a = ops.paged_attn(q, pages, step, heads=self.H, kv_heads=self.G, maps=2, vdim=self.dv, k_off=0, v_off=self.ck, scale=self.scale,
+                           window=self.window)
+        o = ops.diff_combine(a, self.H, self.dv, self.lam, 1.0 - self.diff, self.eps, self.dtype)
+        return ops.linear(o, self.w_o, out_dtype=torch.float32)
+
+
+class BucketBiasAttention(nn.Module):
+    """Grouped-query attention whose values are the keys as projected (there is no value projection), with biases on the q / k
+    projections, queries and keys divided by their RMS per head (no weight), a learned bias rel[bucket(i - j), head] added to the
+    scaled score (`log_distance_buckets` over the table's rows and `bias_max`), and sigmoid(W_g h) multiplied into the concatenated
+    heads before the output projection.  No rotation.  Cache row per token: [unit-RMS keys | keys as projected].
+    Tensors under `prefix`: q, q.b, k, k.b, rel, g, o."""
+
+    def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, scale: float, bias_max: float, eps: float,
+                 window: Optional[int] = None):
+        super().__init__()
+        _need_single_rank(weights, "BucketBiasAttention")
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.H, self.G, self.d, self.scale, self.eps, self.window = heads, kv_heads, dim, float(scale), float(eps), int(window or 0)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_in = torch.cat([get("q"), get("k"), get("g")], 0).contiguous()            # -> [q | k | gate]
+        self.b_in = torch.cat([get("q.b"), get("k.b"), torch.zeros_like(get("q.b"))], 0).contiguous()
+        rel = get("rel")
+        if rel.shape[1] != heads:
+            raise ValueError(f"{prefix}.rel: one column per head expected")
+        self.rel = rel.float().contiguous()
+        self.bucket_tab = torch.tensor(log_distance_buckets(rel.shape[0], float(bias_max)), dtype=torch.int32).to(rel.device)
+        self.w_o = get("o").contiguous()
+        self.dtype = self.w_o.dtype
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="paged", row_width=2 * self.G * self.d)
+
+    def forward(self, h: torch.Tensor, step: ops.RaggedStep, pages: torch.Tensor, state, max_s: int) -> torch.Tensor:
+        H, G, d = self.H, self.G, self.d
+        u = ops.linear(h, self.w_in, self.b_in, out_dtype=torch.float32)
+        q = ops.heads_prepare(u, col_q=0, q_heads=H, dim=d, q_norm_w=None, temp_coef=0.0, temp_every=0, col_k=H * d, k_heads=G, k_norm_w=None,
+                              col_v=H * d, v_width=G * d, normalise=True, step=step, cache=pages, k_off=0, v_off=G * d, eps=self.eps)
+        a = ops.paged_attn(q, pages, step, heads=H, kv_heads=G, maps=1, vdim=d, k_off=0, v_off=G * d, scale=self.scale, window=self.window,
+                           rel=self.rel, bucket_tab=self.bucket_tab)
+        gated = ops.group_rmsnorm_gate(a.view(step.T, H * d), None, 0, self.eps, self.dtype, gate=u[:, (H + G) * d:],
+                                       gate_kind=ops.GATE_SIGMOID_AFTER)
+        return ops.linear(gated, self.w_o, out_dtype=torch.float32)
+
+
+class RoutedExperts(nn.Module):
+    """Mixture of clamped gated experts: router logits in fp32, the `top` largest per token, weights = soft-max over the picked
+    logits; each expert is down(g' sigmoid(alpha g') (u' + 1)) as in `ClampedGatedMLP`, without biases.  `forward` returns the
+    experts' outputs as compact rows (expert by expert) with the routing; `ops.moe_combine_add` sums them into the stream.
+    Tensors under `prefix`: router, e<j>.gate, e<j>.up, e<j>.down."""
+
+    def __init__(self, prefix: str, weights, *, experts: int, top: int, limit: float, alpha: float = 1.702):
+        super().__init__()
+        _need_single_rank(weights, "RoutedExperts")
+        self.E, self.top, self.limit, self.alpha = int(experts), int(top), float(limit), float(alpha)
+        get = lambda n: weights.get_tensor(f"{prefix}.{n}")  # noqa: E731
+        self.w_router = get("router").contiguous()
+        self.w_gate_up = torch.stack([torch.cat([get(f"e{e}.gate"), get(f"e{e}.up")], 0) for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([get(f"e{e}.down") for e in range(self.E)]).contiguous()
+        if self.w_router.shape[0] != self.E:
+            raise ValueError(f"{prefix}.router: one row per expert expected")
+
+    def forward(self, h: torch.Tensor):
+        routing = ops.moe_route(ops.linear(h, self.w_router, out_dtype=torch.float32), self.top)
+        gu = ops.moe_linear(h, self.w_gate_up, routing, gather=True, out_dtype=h.dtype)
+        act = ops.ff_clamped_gate(gu, self.limit, self.alpha)
+        return ops.moe_linear(act, self.w_down, routing, gather=False, out_dtype=torch.float32), routing

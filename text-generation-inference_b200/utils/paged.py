@@ -287,8 +287,9 @@ class PagedKVCacheManager:
 
 @dataclass
 class LayerCacheSpec:
-    """What one layer keeps per sequence: "paged" = `row_width` elements per token in the block pool; "state" = fp32 tensors of
-    the given shapes in the sequence's state slot; "none" = nothing."""
+    """What one layer keeps per sequence: "paged" = `row_width` elements per token in the block pool (and, when `state` is given as
+    well, fp32 tensors in the sequence's state slot: e.g. attention whose projections pass a short convolution); "state" = fp32
+    tensors of the given shapes in the sequence's state slot; "none" = nothing."""
     kind: str = "none"
     row_width: int = 0
     state: Optional[Dict[str, tuple]] = None
@@ -318,16 +319,11 @@ class HybridCacheManager(PagedKVCacheManager):
         self.pages: List[Optional[torch.Tensor]] = []
         self.states: List[Optional[Dict[str, torch.Tensor]]] = []
         for spec in self.layer_specs:
-            if spec.kind == "paged":
-                self.pages.append(torch.zeros(self.total_num_gpu_blocks, block_size, spec.row_width, dtype=dtype, device=self.device))
-                self.states.append(None)
-            elif spec.kind == "state":
-                self.pages.append(None)
-                self.states.append({name: torch.zeros(self.num_state_slots, *shape, dtype=torch.float32, device=self.device)
-                                    for name, shape in spec.state.items()})
-            else:
-                self.pages.append(None)
-                self.states.append(None)
+            paged = spec.kind == "paged" and spec.row_width > 0
+            self.pages.append(torch.zeros(self.total_num_gpu_blocks, block_size, spec.row_width, dtype=dtype, device=self.device)
+                              if paged else None)
+            self.states.append({name: torch.zeros(self.num_state_slots, *shape, dtype=torch.float32, device=self.device)
+                                for name, shape in spec.state.items()} if spec.kind in ("paged", "state") and spec.state else None)
         self._free_slots: List[int] = list(range(self.num_state_slots - 1, -1, -1))  # slot 0 is handed out first
         self._slot_of: Dict[int, int] = {}
         self._init_block_bookkeeping()
@@ -338,6 +334,13 @@ class HybridCacheManager(PagedKVCacheManager):
     def layer_store(self, layer: int):
         """the layer's pool (paged), its dict of state tensors (state) or None"""
         return self.pages[layer] if self.pages[layer] is not None else self.states[layer]
+
+    def layer_pages(self, layer: int) -> Optional[torch.Tensor]:
+        """the layer's pool [blocks, block_size, row_width]; another layer may read it (layers that share keys and values)"""
+        return self.pages[layer]
+
+    def layer_state(self, layer: int) -> Optional[Dict[str, torch.Tensor]]:
+        return self.states[layer]
 
     def block_bytes(self) -> int:
         return sum(p.shape[1] * p.shape[2] * p.element_size() for p in self.pages if p is not None)
