@@ -725,6 +725,81 @@ def _traced_decode_step(model, batch, lib):
     return out, (t[n - 1] - t[0]) / 1e3
 
 
+def _neox_partner(width, PB, PL, DB, DL, K, Wm, timed, hbm, tens, ctx):
+    """GPT-NeoX (fp16, parallel residual, paged attention) with three layers at `width`, measured like the fp32-stream families:
+    the equal-size partner of --hybrid-compare and --dubesun-compare"""
+    import torch
+    from tgis_b200 import ops as ops_f16
+    wl = f"neox-w{width}"
+    nmodel, ncfg = build_model(wl, 1, 0, blocks=(DB + PB) * ((DL + 96) // 16 + 2))
+    tok = nmodel.tokenizer
+    names16 = ["gemm_f16", "layernorm_residual", "rope_kv_write_paged", "attn_prefill_varlen", "attn_decode_paged", "gelu", "embedding",
+               "argmax"]
+
+    def nprefill(B, L, n_new, keep=False):
+        batch, _ = nmodel.batch_type.from_pb(make_batch_pb(B, L, n_new), tok, torch.float16, nmodel.device, None, None, True)
+        nmodel.generate_token(batch, first=True)
+        if keep:
+            return batch
+        nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+    with torch.inference_mode():
+        for _ in range(Wm):
+            nprefill(PB, PL, 2)
+        npre_ms = timed(lambda: nprefill(PB, PL, 2), K)
+        log = []
+        saved = _timed_ops(ops_f16, names16, log)
+        nprefill(PB, PL, 2)
+        npre_ops = _by_op(log)
+        for n, fn in saved.items():
+            setattr(ops_f16, n, fn)
+        os.environ["B200_PY_FUSED_STEP"] = "0"  # op by op, as the hybrid model runs: like is compared with like
+        batch = nprefill(DB, DL, Wm + K + 8, keep=True)
+        for _ in range(Wm):
+            nmodel.generate_token(batch)
+        ndec_ms = timed(lambda: nmodel.generate_token(batch), K)
+        log = []
+        saved = _timed_ops(ops_f16, names16, log)
+        nmodel.generate_token(batch)
+        ndec_ops = _by_op(log)
+        for n, fn in saved.items():
+            setattr(ops_f16, n, fn)
+        os.environ.pop("B200_PY_FUSED_STEP", None)
+        nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+        batch = nprefill(DB, DL, Wm + K + 8, keep=True)  # and as served: the graph-replayed step
+        for _ in range(Wm):
+            nmodel.generate_token(batch)
+        ngraph_ms = timed(lambda: nmodel.generate_token(batch), K)
+        from tgis_b200 import _lib as _libmod
+        ndec_k, ndec_total = _traced_decode_step(nmodel, batch, _libmod.load())
+        nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
+    hd, nh = 128, width // 128
+    nattn_flops = PB * 4 * (PL * PL // 2) * hd * nh
+    nlin_w = 3 * (4 * width * width + 2 * width * 4 * width) + ncfg.vocab_size * width
+    nkernels = {
+        "attn_prefill_varlen": {"ms": npre_ops.get("attn_prefill_varlen", 0.0),
+                                "of_measured_tensor": nattn_flops / (max(npre_ops.get("attn_prefill_varlen", 0.0), 1e-9) * 1e-3) / tens},
+        "attn_decode_paged": {"us": ndec_k.get("attn_decode_paged_kernel", 0.0) + ndec_k.get("attn_decode_combine_kernel", 0.0), "of_measured_hbm":
+                              3 * DB * ctx * 2 * nh * hd * 2
+                              / ((ndec_k.get("attn_decode_paged_kernel", 1e-9) + ndec_k.get("attn_decode_combine_kernel", 0.0)) * 1e-6) / hbm},
+        "gemm_f16 prefill (all projections)": {"ms": npre_ops["gemm_f16"], "of_measured_tensor":
+                                               (2 * PB * PL * (nlin_w - ncfg.vocab_size * width) + 2 * PB * ncfg.vocab_size * width)
+                                               / (npre_ops["gemm_f16"] * 1e-3) / tens},
+        "gemm_f16 decode (all projections)": {"us": ndec_k["gemm_f16_kernel"], "of_measured_hbm": nlin_w * 2 / (ndec_k["gemm_f16_kernel"] * 1e-6) / hbm},
+    }
+    result = ({"model": wl, "dtype": "fp16", "layers": 3, "prefill_tokens_per_s": PB * PL / (npre_ms * 1e-3),
+                    "decode_tokens_per_s": DB / (ndec_ms * 1e-3), "prefill_ms": npre_ms, "decode_ms_per_step": ndec_ms,
+                    "decode_mode": "op by op (B200_PY_FUSED_STEP=0)",
+                    "decode_graph_tokens_per_s": DB / (ngraph_ms * 1e-3), "decode_graph_ms_per_step": ngraph_ms,
+                    "prefill_ms_by_op": {k: round(v, 4) for k, v in npre_ops.items()},
+                    "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()},
+                    "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(ndec_k.items(), key=lambda kv: -kv[1])},
+                    "decode_graph_traced_us": ndec_total, "kernels": nkernels})
+    del nmodel
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
 def run_hybrid_compare(args):
     """Fetotar (bfloat16) beside GPT-NeoX (fp16) at equal width and depth, random weights: prefill of 4 x 1024 tokens and decode of
     32 sequences at context 1024.  Per model: tokens/s through the engine's own step (device time by CUDA events, L2 flushed
@@ -850,74 +925,7 @@ def run_hybrid_compare(args):
         gc.collect()
         torch.cuda.empty_cache()
 
-        # ---------------------------------------------------------------- the equal-size GPT-NeoX partner
-        wl = f"neox-w{width}"
-        nmodel, ncfg = build_model(wl, 1, 0, blocks=(DB + PB) * ((DL + 96) // 16 + 2))
-        tok = nmodel.tokenizer
-        names16 = ["gemm_f16", "layernorm_residual", "rope_kv_write_paged", "attn_prefill_varlen", "attn_decode_paged", "gelu", "embedding",
-                   "argmax"]
-
-        def nprefill(B, L, n_new, keep=False):
-            batch, _ = nmodel.batch_type.from_pb(make_batch_pb(B, L, n_new), tok, torch.float16, nmodel.device, None, None, True)
-            nmodel.generate_token(batch, first=True)
-            if keep:
-                return batch
-            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
-        with torch.inference_mode():
-            for _ in range(Wm):
-                nprefill(PB, PL, 2)
-            npre_ms = timed(lambda: nprefill(PB, PL, 2), K)
-            log = []
-            saved = _timed_ops(ops_f16, names16, log)
-            nprefill(PB, PL, 2)
-            npre_ops = _by_op(log)
-            for n, fn in saved.items():
-                setattr(ops_f16, n, fn)
-            os.environ["B200_PY_FUSED_STEP"] = "0"  # op by op, as the hybrid model runs: like is compared with like
-            batch = nprefill(DB, DL, Wm + K + 8, keep=True)
-            for _ in range(Wm):
-                nmodel.generate_token(batch)
-            ndec_ms = timed(lambda: nmodel.generate_token(batch), K)
-            log = []
-            saved = _timed_ops(ops_f16, names16, log)
-            nmodel.generate_token(batch)
-            ndec_ops = _by_op(log)
-            for n, fn in saved.items():
-                setattr(ops_f16, n, fn)
-            os.environ.pop("B200_PY_FUSED_STEP", None)
-            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
-            batch = nprefill(DB, DL, Wm + K + 8, keep=True)  # and as served: the graph-replayed step
-            for _ in range(Wm):
-                nmodel.generate_token(batch)
-            ngraph_ms = timed(lambda: nmodel.generate_token(batch), K)
-            from tgis_b200 import _lib as _libmod
-            ndec_k, ndec_total = _traced_decode_step(nmodel, batch, _libmod.load())
-            nmodel.kv_cache_manager.free_sequences(batch.sequence_ids)
-        hd, nh = 128, width // 128
-        nattn_flops = PB * 4 * (PL * PL // 2) * hd * nh
-        nlin_w = 3 * (4 * width * width + 2 * width * 4 * width) + ncfg.vocab_size * width
-        nkernels = {
-            "attn_prefill_varlen": {"ms": npre_ops.get("attn_prefill_varlen", 0.0),
-                                    "of_measured_tensor": nattn_flops / (max(npre_ops.get("attn_prefill_varlen", 0.0), 1e-9) * 1e-3) / tens},
-            "attn_decode_paged": {"us": ndec_k.get("attn_decode_paged_kernel", 0.0) + ndec_k.get("attn_decode_combine_kernel", 0.0), "of_measured_hbm":
-                                  3 * DB * ctx * 2 * nh * hd * 2
-                                  / ((ndec_k.get("attn_decode_paged_kernel", 1e-9) + ndec_k.get("attn_decode_combine_kernel", 0.0)) * 1e-6) / hbm},
-            "gemm_f16 prefill (all projections)": {"ms": npre_ops["gemm_f16"], "of_measured_tensor":
-                                                   (2 * PB * PL * (nlin_w - ncfg.vocab_size * width) + 2 * PB * ncfg.vocab_size * width)
-                                                   / (npre_ops["gemm_f16"] * 1e-3) / tens},
-            "gemm_f16 decode (all projections)": {"us": ndec_k["gemm_f16_kernel"], "of_measured_hbm": nlin_w * 2 / (ndec_k["gemm_f16_kernel"] * 1e-6) / hbm},
-        }
-        results.append({"model": wl, "dtype": "fp16", "layers": 3, "prefill_tokens_per_s": PB * PL / (npre_ms * 1e-3),
-                        "decode_tokens_per_s": DB / (ndec_ms * 1e-3), "prefill_ms": npre_ms, "decode_ms_per_step": ndec_ms,
-                        "decode_mode": "op by op (B200_PY_FUSED_STEP=0)",
-                        "decode_graph_tokens_per_s": DB / (ngraph_ms * 1e-3), "decode_graph_ms_per_step": ngraph_ms,
-                        "prefill_ms_by_op": {k: round(v, 4) for k, v in npre_ops.items()},
-                        "decode_ms_by_op": {k: round(v, 4) for k, v in ndec_ops.items()},
-                        "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(ndec_k.items(), key=lambda kv: -kv[1])},
-                        "decode_graph_traced_us": ndec_total, "kernels": nkernels})
-        del nmodel
-        gc.collect()
-        torch.cuda.empty_cache()
+        results.append(_neox_partner(width, PB, PL, DB, DL, K, Wm, timed, hbm, tens, ctx))
     kernels["latent_attn decode"]["note"] = "3 attention layers in the partner vs 1 latent-attention layer here: compare fractions, not ms"
     print(json.dumps({"metric": "hybrid_compare", "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": Wm, "data": "synthetic",
                       "config": {"prefill": [PB, PL], "decode": [DB, DL], "l2": "flushed between timed calls"},

@@ -89,9 +89,9 @@ int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int 
 /* soft-max attention of H * maps query rows per token over G * maps paged key heads (d) and G value heads (dv) of its own sequence,
  * causal, optional window, optional bias rel[bucket(distance), head] (fp32 [rel_rows, H]) after the scale; out fp32 [Tq, H * maps, dv] */
 int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
-                        int64_t bt_stride, const int32_t* seq_of_token, const int64_t* position_ids, float* out, int64_t Tq, int H, int G,
-                        int maps, int d, int dv, int window, float scale, int page, const float* rel, const int32_t* bucket_tab,
-                        int n_bucket_tab, int rel_rows, void* stream);
+                        int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids, float* out,
+                        int64_t Tq, int H, int G, int maps, int d, int dv, int window, float scale, int page, const float* rel,
+                        const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, void* stream);
 /* in fp32 [T, H, 2, dv] -> out [T, H * dv]: (a1 - lambda a2) / sqrt(mean(.^2) + eps) * out_scale */
 int b200_seq_diff_combine(const float* in, void* out, int out_dt, int64_t T, int H, int dv, float lambda, float out_scale, float eps,
                           void* stream);
@@ -102,6 +102,8 @@ int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* 
 /* C[row] = W[expert(row)] A[gather ? token(row) : row] for the T * top rows of the plan; W [E, N, K] */
 int b200_seq_moe_linear(const void* A, int a_dt, int64_t lda, int gather, const void* W, int w_dt, void* C, int c_dt, int64_t ldc,
                         int32_t* plan, int64_t T, int E, int top, int64_t N, int64_t K, void* stream);
+/* out [T * top, K] = A[token(row)]: compact rows for callers that run one dense product per expert (plan offsets at int E of plan) */
+int b200_seq_moe_gather_rows(const void* A, int dt, int64_t lda, void* out, int32_t* plan, int64_t T, int E, int top, int64_t K, void* stream);
 /* resid += mix + sum_k weights[t, k] y[row(t, k)]; mix and y may be NULL */
 int b200_seq_moe_combine_add(float* resid, const float* mix, const float* y, int64_t ldy, const float* weights, int32_t* plan, int64_t T,
                              int E, int top, int64_t W, void* stream);

@@ -8,11 +8,14 @@
 //   moe_linear_kernel  : C[row] = W[expert of row's tile] A[row] over that plan; A rows are either the compact rows or gathered
 //                        through the row -> token map.  fp32 accumulation in ascending k: a row's result does not depend on what
 //                        else the step holds.
+//   moe_linear_mma_kernel : the same product on tensor cores for bfloat16 operands (see the note above the kernel).
 //   moe_combine_add_kernel : resid[t] += mix[t] + sum over the token's picks, in pick order, of weight * y[row(t, pick)].
 //
 // Plan workspace (int32): [counts E][offsets E + 1][n_tiles 1][tile_expert max_tiles][tile_row0 max_tiles][place R][row_of R]
 // [token_of_row R] with R = T * top and max_tiles = ceil(R / 64) + E.
 #include "seq_common.cuh"
+
+#include <cstdlib>
 
 namespace b200 {
 namespace seq {
@@ -180,6 +183,103 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(const TA* __restrict__ 
   }
 }
 
+// Tensor-core form of moe_linear_kernel for bfloat16 operands: 64 x 64 output tile per block of four warps (each 32 x 32), k in
+// steps of 64 through a three-stage cp.async pipeline, m16n8k16 products with fp32 accumulation in ascending k.  With the few
+// rows per expert of a decoding step the work is streaming each picked expert's weights once; the tiles of the plan keep that
+// to the experts that were picked.  Needs K % 8 == 0 and 16-byte aligned rows.
+constexpr int kMmaBK = 64, kMmaStages = 3, kMmaLd = kMmaBK + 8;
+
+template <typename TC>
+__global__ void __launch_bounds__(128) moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, int gather,
+                                                             const __nv_bfloat16* __restrict__ W, TC* __restrict__ C, int64_t ldc, MoePlan p, int N,
+                                                             int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // [stages][64][kMmaLd]
+  __nv_bfloat16* Ws = As + kMmaStages * kMoeTile * kMmaLd;             // [stages][64][kMmaLd]
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;
+  const int e = p.tile_expert[tile], m0 = p.tile_row0[tile], m_end = p.offsets[e + 1];
+  W += (int64_t)e * N * K;
+  const int n0 = blockIdx.x * kMoeTile;
+  const int tid = threadIdx.x, w = warp_id(), lane = lane_id();
+  // loader: chunk c = tid + 128 i covers row c / 8, k offset (c % 8) * 8 of the 64 x 64 tile
+  const int kc = (tid & 7) * 8;
+  const __nv_bfloat16* a_src[4];
+  const __nv_bfloat16* w_src[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = (tid >> 3) + i * 16;
+    const int m = m0 + row, n = n0 + row;
+    a_src[i] = m < m_end ? A + (gather ? (int64_t)p.token_of_row[m] : (int64_t)m) * lda : nullptr;
+    w_src[i] = n < N ? W + (int64_t)n * K : nullptr;
+  }
+  auto load = [&](int stage, int kt) {
+    const int k = kt * kMmaBK + kc;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = (tid >> 3) + i * 16;
+      const bool pa = a_src[i] != nullptr && k < K, pw = w_src[i] != nullptr && k < K;
+      cp_async_16(As + (stage * kMoeTile + row) * kMmaLd + kc, pa ? a_src[i] + k : A, pa);
+      cp_async_16(Ws + (stage * kMoeTile + row) * kMmaLd + kc, pw ? w_src[i] + k : W, pw);
+    }
+    cp_async_commit();
+  };
+  const int nk = (K + kMmaBK - 1) / kMmaBK;
+  load(0, 0);
+  if (nk > 1) load(1, 1);
+  float acc[2][4][4] = {};
+  const int wm = w >> 1, wn = w & 1, lm = lane >> 3, lr = lane & 7;
+  const uint32_t as_addr = smem_u32(As), ws_addr = smem_u32(Ws);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int stage = kt % kMmaStages;
+    if (kt + 1 < nk) cp_async_wait<1>();
+    else cp_async_wait<0>();
+    __syncthreads();  // stage kt has landed; everyone is done with the stage that the next load overwrites
+    if (kt + 2 < nk) load((kt + 2) % kMmaStages, kt + 2);
+    const uint32_t a_lane = as_addr + (uint32_t)(((stage * kMoeTile + wm * 32 + (lm & 1) * 8 + lr) * kMmaLd + (lm >> 1) * 8) * 2);
+    const uint32_t b_lane = ws_addr + (uint32_t)(((stage * kMoeTile + wn * 32 + (lm >> 1) * 8 + lr) * kMmaLd + (lm & 1) * 8) * 2);
+#pragma unroll
+    for (int kk = 0; kk < kMmaBK; kk += 16) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3], a_lane + (uint32_t)((mt * 16 * kMmaLd + kk) * 2));
+#pragma unroll
+      for (int np = 0; np < 2; ++np) ldmatrix_x4(b[np][0], b[np][1], b[np][2], b[np][3], b_lane + (uint32_t)((np * 16 * kMmaLd + kk) * 2));
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          mma_m16n8k16_bf16f32(acc[mt][2 * np], a[mt], b[np][0], b[np][1]);
+          mma_m16n8k16_bf16f32(acc[mt][2 * np + 1], a[mt], b[np][2], b[np][3]);
+        }
+    }
+  }
+  const int cq = (lane & 3) * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int el = 0; el < 4; ++el) {
+        const int m = m0 + wm * 32 + mt * 16 + (lane >> 2) + (el >> 1) * 8;
+        const int n = n0 + wn * 32 + nt * 8 + cq + (el & 1);
+        if (m < m_end && n < N) stf(C + (int64_t)m * ldc + n, acc[mt][nt][el]);
+      }
+}
+
+// out[row] = A[token(row)] for the compact rows of the plan (what a dense product per expert reads)
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gather_rows_kernel(const T* __restrict__ A, int64_t lda, T* __restrict__ out, const int32_t* __restrict__ token_of_row,
+                                                              int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const T* src = A + (int64_t)token_of_row[row] * lda;
+  for (int i = threadIdx.x; i < K; i += 256) out[row * K + i] = src[i];
+}
+
 // top == 0 (or y == nullptr): resid += mix only
 __global__ void __launch_bounds__(256) moe_combine_add_kernel(float* __restrict__ resid, const float* __restrict__ mix, const float* __restrict__ y,
                                                               int64_t ldy, const float* __restrict__ weights, const int32_t* __restrict__ row_of,
@@ -235,6 +335,24 @@ extern "C" int b200_seq_moe_linear(const void* A, int a_dt, int64_t lda, int gat
   MoePlan p = moe_plan_view(plan, T, E, top);
   if (p.max_tiles > 65535 || K <= 0) { b200_set_last_error("seq_moe_linear: bad sizes"); return B200_ERR_ARG; }
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_MOE_MMA"); return !(e && e[0] == '0'); }();
+  if (use_mma && a_dt == B200_DT_BF16 && w_dt == B200_DT_BF16 && K % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(W) & 15) == 0) {
+    const size_t smem = (size_t)2 * kMmaStages * kMoeTile * kMmaLd * 2;
+    dim3 grid((unsigned)((N + kMoeTile - 1) / kMoeTile), (unsigned)p.max_tiles);
+#define MMA_LAUNCH(TC)                                                                                                                  \
+  do {                                                                                                                                  \
+    static bool cfg = false;                                                                                                            \
+    if (!cfg) { cudaFuncSetAttribute(moe_linear_mma_kernel<TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); cfg = true; }   \
+    B200_LAUNCH((moe_linear_mma_kernel<TC>), grid, dim3(128), smem, st, (const __nv_bfloat16*)A, lda, gather, (const __nv_bfloat16*)W,   \
+                (TC*)C, ldc, p, (int)N, (int)K);                                                                                        \
+    b200_count_launches(1);                                                                                                             \
+    return B200_OK;                                                                                                                     \
+  } while (0)
+    if (c_dt == B200_DT_F32) MMA_LAUNCH(float);
+    else MMA_LAUNCH(__nv_bfloat16);
+#undef MMA_LAUNCH
+  }
   const int key = a_dt * 4 + w_dt * 2 + c_dt;
 #define CASE(a, w, c, TA, TW, TC) \
   case a * 4 + w * 2 + c: return launch_moe_linear<TA, TW, TC>(A, lda, gather, W, C, ldc, p, N, K, st)
@@ -258,6 +376,17 @@ extern "C" int b200_seq_moe_combine_add(float* resid, const float* mix, const fl
   if (y != nullptr && top > 0) row_of = moe_plan_view(plan, T, E, top).row_of;
   else top = 0;
   B200_LAUNCH(moe_combine_add_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, resid, mix, y, ldy, weights, row_of, top, (int)W);
+  b200_count_launches(1);
+  return B200_OK;
+}
+
+// out [T * top, K] (type dt) = A[token(row)]: the compact rows, for callers that run one dense product per expert
+extern "C" int b200_seq_moe_gather_rows(const void* A, int dt, int64_t lda, void* out, int32_t* plan, int64_t T, int E, int top, int64_t K,
+                                        void* stream) {
+  if (T == 0) return B200_OK;
+  MoePlan p = moe_plan_view(plan, T, E, top);
+  B200_SEQ_DISPATCH(dt, El, B200_LAUNCH((moe_gather_rows_kernel<El>), dim3((unsigned)(T * top)), dim3(256), 0, (cudaStream_t)stream, (const El*)A, lda,
+                                        (El*)out, (const int32_t*)p.token_of_row, (int)K));
   b200_count_launches(1);
   return B200_OK;
 }

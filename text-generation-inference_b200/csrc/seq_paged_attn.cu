@@ -10,6 +10,8 @@
 //                          warp; key tiles of 32 rows pass through shared memory, fp32 online soft-max.  Optional learned bias per
 //                          (distance bucket, head), added after the scale; optional sliding window.  Prompts, portions of prompts
 //                          and decoded tokens are the same case: every key is read back from the cache.
+//   paged_heads_attn_mma_kernel : the same on bfloat16 caches with m16n8k16 tensor-core products; one block per (sequence, key/value
+//                          head, tile of query tokens), rows = (map, token, query head of the group); see the note above the kernel.
 //   diff_combine_kernel  : o = a1 - lambda a2 per head, o / sqrt(mean(o^2) + eps) * out_scale.
 #include "seq_common.cuh"
 
@@ -169,6 +171,203 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_heads_attn_kernel(
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// Tensor-core form for bfloat16 caches.  One block of four warps per (sequence, key/value head, tile of query tokens): its 64
+// rows are (map, token of the tile, query head of the group), map-major, so a warp's 16 rows share one map and read that map's
+// key columns; both maps read the same value tile, which is loaded once.  Key / value tiles of KT rows come in with 16-byte
+// cp.async, two stages deep; S = Q K^T and O += P V are m16n8k16 products, each warp keeps the running max, sum and output of
+// its own rows in registers (no exchange between warps), P stays in registers between the two products.  Bias and masks are
+// applied to S per element, so a tile may mix tokens at different positions.  Needs dim % 16 == 0, vdim % 16 == 0,
+// vdim <= 256, (heads / kv_heads) * maps dividing 64 and 16-byte aligned head slices; everything else takes the plain kernel.
+// ------------------------------------------------------------------------------------------------------------------------
+constexpr int kMmaRows = 64, kMmaThreads = 128, kMmaPad = 8;
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int NDV, int KT>  // NDV = vdim / 8 output n-tiles per warp, KT keys per tile
+__global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
+    const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
+    int64_t bt_stride, const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ out, int B, int H, int rep,
+    int maps, int d, int window, float scale, int page, const float* __restrict__ rel, const int32_t* __restrict__ bucket_tab, int n_bucket_tab,
+    int rel_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int dv = NDV * 8, VP = dv + kMmaPad;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int KD = maps * d, KP = KD + kMmaPad, DP = d + kMmaPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][DP]
+  __nv_bfloat16* Ks = Qs + kMmaRows * DP;                            // [2][KT][KP]
+  __nv_bfloat16* Vs = Ks + 2 * KT * KP;                              // [2][KT][VP]
+  const int rpm = kMmaRows / maps;   // rows per map
+  const int QT = rpm / rep;          // query tokens per tile
+  // which (sequence, tile of its tokens) this block has
+  int tile = blockIdx.x, b = 0;
+  for (; b < B; ++b) {
+    const int nt = (cu_q[b + 1] - cu_q[b] + QT - 1) / QT;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (b >= B) return;
+  const int g = blockIdx.y;
+  const int row0 = cu_q[b] + tile * QT;
+  const int ntok = min(QT, cu_q[b + 1] - row0);
+  const int p0 = (int)position_ids[row0], p_last = p0 + ntok - 1;
+  const int j_start = max(0, p0 - window + 1);
+  const int w = warp_id(), lane = lane_id();
+  const int Hq = H * maps;
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  for (int idx = threadIdx.x; idx < kMmaRows * d; idx += kMmaThreads) {
+    const int r = idx / d, c = idx % d;
+    const int mp = r / rpm, rr = r % rpm, tok = rr / rep, hh = rr % rep;
+    float v = 0.f;
+    if (tok < ntok) v = q[((int64_t)(row0 + tok) * Hq + (g * rep + hh) * maps + mp) * d + c] * scale;
+    Qs[r * DP + c] = __float2bfloat16_rn(v);
+  }
+  const int kchunks = KD / 8, vchunks = dv / 8, cpr = kchunks + vchunks;
+  auto load_tile = [&](int stage, int j0) {
+    __nv_bfloat16* kd = Ks + stage * KT * KP;
+    __nv_bfloat16* vd = Vs + stage * KT * VP;
+    for (int idx = threadIdx.x; idx < KT * cpr; idx += kMmaThreads) {
+      const int row = idx / cpr, ch = idx % cpr, j = j0 + row;
+      __nv_bfloat16* dst = ch < kchunks ? kd + row * KP + ch * 8 : vd + row * VP + (ch - kchunks) * 8;
+      if (j <= p_last) {
+        const __nv_bfloat16* src = cache + ((int64_t)table[j / page] * page + j % page) * RW;
+        src += ch < kchunks ? k_off + (int64_t)g * KD + ch * 8 : v_off + (int64_t)g * dv + (ch - kchunks) * 8;
+        cp_async_16(dst, src, true);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);  // finite: these rows meet p = 0
+      }
+    }
+    cp_async_commit();
+  };
+  // this thread's two accumulator rows
+  const int cq = (lane & 3) * 2;
+  int p_row[2], h_row[2];
+  bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = w * 16 + (lane >> 2) + i * 8, rr = r % rpm, tok = rr / rep;
+    valid[i] = tok < ntok;
+    p_row[i] = valid[i] ? p0 + tok : p0;
+    h_row[i] = g * rep + rr % rep;
+  }
+  const int mp_w = (w * 16) / rpm;
+  const bool warp_active = ((w * 16) % rpm) / rep < ntok;  // rows of a warp ascend in token: its first row decides
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[NDV][4];
+#pragma unroll
+  for (int i = 0; i < NDV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+  const int lm = lane >> 3, lr = lane & 7;
+  const uint32_t a_lane = qs_addr + (uint32_t)(((w * 16 + (lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
+  int stage = 0;
+  load_tile(0, j_start);
+  for (int j0 = j_start; j0 <= p_last; j0 += KT, stage ^= 1) {
+    if (j0 + KT <= p_last) {
+      load_tile(stage ^ 1, j0 + KT);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();  // the tile (and, first time round, Qs) is in shared memory
+    if (warp_active) {
+      float s[KT / 8][4];
+#pragma unroll
+      for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      const uint32_t b_lane = ks_addr + (uint32_t)(((stage * KT + (lm >> 1) * 8 + lr) * KP + mp_w * d + (lm & 1) * 8) * 2);
+      for (int kk = 0; kk < d; kk += 16) {
+        uint32_t a[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
+#pragma unroll
+        for (int kg = 0; kg < KT / 16; ++kg) {
+          uint32_t bb[4];
+          ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)((kg * 16 * KP + kk) * 2));
+          mma_m16n8k16_bf16f32(s[2 * kg], a, bb[0], bb[1]);
+          mma_m16n8k16_bf16f32(s[2 * kg + 1], a, bb[2], bb[3]);
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
+          const int dist = p_row[i] - j;
+          float v = s[nt][e];
+          if (dist < 0 || dist >= window) {
+            v = -INFINITY;
+          } else if (rel) {
+            v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+          }
+          s[nt][e] = v;
+          mx[i] = fmaxf(mx[i], v);
+        }
+      float m_use[2], corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        const float m_new = fmaxf(m_run[i], mx[i]);
+        m_use[i] = m_new == -INFINITY ? 0.f : m_new;  // a row that has met no visible key yet
+        corr[i] = expf(m_run[i] - m_use[i]);
+        m_run[i] = m_new;
+      }
+      uint32_t pa[KT / 16][4];
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(expf(s[nt][0] - m_use[0]), expf(s[nt][1] - m_use[0]));
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(expf(s[nt][2] - m_use[1]), expf(s[nt][3] - m_use[1]));
+        // the sums use the rounded probabilities: numerator and denominator see the same weights
+        sum[0] += __low2float(lo) + __high2float(lo);
+        sum[1] += __low2float(hi) + __high2float(hi);
+        pa[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&lo);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+        sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+        l_run[i] = l_run[i] * corr[i] + sum[i];
+      }
+#pragma unroll
+      for (int i = 0; i < NDV; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      const uint32_t v_lane = vs_addr + (uint32_t)(((stage * KT + (lm & 1) * 8 + lr) * VP + (lm >> 1) * 8) * 2);
+#pragma unroll
+      for (int kg = 0; kg < KT / 16; ++kg) {
+#pragma unroll
+        for (int nt = 0; nt < NDV; nt += 2) {
+          uint32_t bb[4];
+          ldmatrix_x4_trans(bb[0], bb[1], bb[2], bb[3], v_lane + (uint32_t)((kg * 16 * VP + nt * 8) * 2));
+          mma_m16n8k16_bf16f32(o[nt], pa[kg], bb[0], bb[1]);
+          mma_m16n8k16_bf16f32(o[nt + 1], pa[kg], bb[2], bb[3]);
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with this stage before the load after next overwrites it
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!valid[i]) continue;
+    const int r = w * 16 + (lane >> 2) + i * 8, rr = r % rpm;
+    const int qh = (g * rep + rr % rep) * maps + r / rpm;
+    float* dst = out + ((int64_t)(row0 + rr / rep) * Hq + qh) * dv;
+    const float inv = 1.f / l_run[i];
+#pragma unroll
+    for (int nt = 0; nt < NDV; ++nt) {
+      dst[nt * 8 + cq] = o[nt][i * 2] * inv;
+      dst[nt * 8 + cq + 1] = o[nt][i * 2 + 1] * inv;
+    }
+  }
+}
+
 // in [T, H, 2, dv] fp32 (two maps per head) -> out [T, H * dv]: o = a1 - lambda a2, unit RMS over dv, times out_scale
 template <typename TO>
 __global__ void __launch_bounds__(256) diff_combine_kernel(const float* __restrict__ in, TO* __restrict__ out, int H, int dv, float lambda,
@@ -232,10 +431,12 @@ static int launch_paged_heads_attn(const float* q, const void* cache, int64_t RW
 // heads of d elements from k_off (key head g, map m at g * maps + m) and G value heads of dv elements from v_off; out fp32
 // [Tq, H * maps, dv].  window <= 0: every earlier token is visible.  rel (fp32 [rel_rows, H]) NULL: no bias; otherwise
 // rel[bucket(distance), h] is added to the scaled score, bucket(n) = bucket_tab[n] for n < n_bucket_tab and rel_rows - 1 beyond.
+// cu_q [B + 1]: row boundaries of the step's sequences (the tensor-core kernel tiles a sequence's rows; NULL: plain kernel only).
 extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off,
-                                   const int32_t* block_table, int64_t bt_stride, const int32_t* seq_of_token, const int64_t* position_ids,
-                                   float* out, int64_t Tq, int H, int G, int maps, int d, int dv, int window, float scale, int page,
-                                   const float* rel, const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, void* stream) {
+                                   const int32_t* block_table, int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B,
+                                   const int64_t* position_ids, float* out, int64_t Tq, int H, int G, int maps, int d, int dv, int window,
+                                   float scale, int page, const float* rel, const int32_t* bucket_tab, int n_bucket_tab, int rel_rows,
+                                   void* stream) {
   if (Tq == 0) return B200_OK;
   if (G <= 0 || H % G != 0 || maps < 1 || d <= 0 || dv <= 0 || dv > 512) {
     b200_set_last_error("seq_paged_attn: need heads % kv_heads == 0, maps >= 1, 0 < vdim <= 512");
@@ -244,6 +445,47 @@ extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, in
   if (window <= 0) window = 0x3fffffff;
   cudaStream_t st = (cudaStream_t)stream;
   const int rows_g = (H / G) * maps;
+  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_ATTN_MMA"); return !(e && e[0] == '0'); }();
+  if (use_mma && dt == B200_DT_BF16 && cu_q != nullptr && maps <= 2 && kMmaRows % rows_g == 0 && d % 16 == 0 && dv % 16 == 0 && dv <= 256 &&
+      row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+    const int QT = kMmaRows / rows_g;
+    const int64_t tiles = (Tq + QT - 1) / QT + B;  // upper bound of sum_b ceil(n_b / QT); surplus blocks return at once
+    const int kt = dv <= 128 ? 64 : 32;
+    const size_t smem = ((size_t)kMmaRows * (d + kMmaPad) + 2 * (size_t)kt * (maps * d + kMmaPad) + 2 * (size_t)kt * (dv + kMmaPad)) * 2;
+    if (smem <= 200 * 1024 && tiles <= 0x7fffffff) {
+      dim3 grid((unsigned)tiles, (unsigned)G);
+#define PAM(N, KT)                                                                                                                       \
+  do {                                                                                                                                   \
+    static bool cfg = false;                                                                                                             \
+    if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_mma_kernel<N, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
+    B200_LAUNCH((paged_heads_attn_mma_kernel<N, KT>), grid, dim3(kMmaThreads), smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
+                block_table, bt_stride, cu_q, position_ids, out, B, H, H / G, maps, d, window, scale, page, rel, bucket_tab, n_bucket_tab,  \
+                rel_rows);                                                                                                               \
+    b200_count_launches(1);                                                                                                              \
+    return B200_OK;                                                                                                                      \
+  } while (0)
+      switch (dv / 8) {
+        case 2: PAM(2, 64);
+        case 4: PAM(4, 64);
+        case 6: PAM(6, 64);
+        case 8: PAM(8, 64);
+        case 10: PAM(10, 64);
+        case 12: PAM(12, 64);
+        case 14: PAM(14, 64);
+        case 16: PAM(16, 64);
+        case 18: PAM(18, 32);
+        case 20: PAM(20, 32);
+        case 22: PAM(22, 32);
+        case 24: PAM(24, 32);
+        case 26: PAM(26, 32);
+        case 28: PAM(28, 32);
+        case 30: PAM(30, 32);
+        case 32: PAM(32, 32);
+        default: break;
+      }
+#undef PAM
+    }
+  }
   const int nv = (dv + 31) / 32;
 #define PA(RPW, NV)                                                                                                                      \
   B200_SEQ_DISPATCH(dt, E, return (launch_paged_heads_attn<E, RPW, NV>(q, cache, row_width, k_off, v_off, block_table, bt_stride, seq_of_token, \

@@ -341,9 +341,13 @@ class FlashCausalLM(Model):
                           slot_mapping=mgr.slot_mapping_for(sids, starts, counts), max_blocks=0,
                           state_slots=mgr.state_slots_tensor(sids) if hasattr(mgr, "state_slots_tensor") else None)
         rows = None if logits_rows is None else torch.tensor(logits_rows, dtype=torch.int64).to(dev, non_blocking=True)
-        with self.context_manager():
-            logits, _ = self.model.forward(flat.to(dev, non_blocking=True), pos.to(dev, non_blocking=True), None,
-                                           cu_q.to(dev, non_blocking=True), max(ends), None, kv, None, rows)
+        try:
+            with self.context_manager():
+                logits, _ = self.model.forward(flat.to(dev, non_blocking=True), pos.to(dev, non_blocking=True), None,
+                                               cu_q.to(dev, non_blocking=True), max(ends), None, kv, None, rows)
+        except BaseException:
+            mgr.free_sequences([sids[i] for i in fresh])  # a step the model refuses (e.g. too many positions) admits nobody
+            raise
         return sids, logits
 
     def _decode_advance(self, batch) -> None:

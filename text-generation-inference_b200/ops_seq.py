@@ -320,7 +320,8 @@ def paged_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, heads:
     out = torch.empty(T, Hq, vdim, dtype=torch.float32, device=q.device)
     _lib.check_seq(_lib.load_seq().b200_seq_paged_attn(
         _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
-        _ptr(step.seq_of_token), _ptr(step.position_ids), _ptr(out), T, heads, kv_heads, maps, d, vdim, int(window), float(scale),
+        _ptr(step.seq_of_token), _ptr(step.cu_q), step.B, _ptr(step.position_ids), _ptr(out), T, heads, kv_heads, maps, d, vdim, int(window),
+        float(scale),
         cache.shape[1], _ptr(rel), _ptr(bucket_tab), 0 if bucket_tab is None else bucket_tab.shape[0], 0 if rel is None else rel.shape[0],
         _stream()), "seq_paged_attn")
     return out
@@ -370,6 +371,21 @@ def moe_linear(a: torch.Tensor, w: torch.Tensor, r: MoeRouting, gather: bool, ou
     _lib.check_seq(_lib.load_seq().b200_seq_moe_linear(_ptr(a), _dt(a), a.stride(0), int(gather), _ptr(w), _dt(w), _ptr(out), _dt(out),
                                                        out.stride(0), _ptr(r.plan), r.T, E, r.top, N, K, _stream()), "seq_moe_linear")
     return out
+
+
+def moe_gather_rows(a: torch.Tensor, r: MoeRouting) -> torch.Tensor:
+    """a [T, K] -> [T * top, K]: the compact rows (row i holds the token of pick i in expert order), for one dense product per expert."""
+    _cuda(a)
+    assert a.stride(1) == 1 and a.shape[0] == r.T
+    out = torch.empty(r.T * r.top, a.shape[1], dtype=a.dtype, device=a.device)
+    _lib.check_seq(_lib.load_seq().b200_seq_moe_gather_rows(_ptr(a), _dt(a), a.stride(0), _ptr(out), _ptr(r.plan), r.T, r.experts, r.top, a.shape[1],
+                                                            _stream()), "seq_moe_gather_rows")
+    return out
+
+
+def moe_expert_offsets(r: MoeRouting) -> list:
+    """first compact row of every expert, and the row count at the end (a device-to-host read: not inside a captured graph)"""
+    return r.plan[r.experts:2 * r.experts + 1].tolist()
 
 
 def moe_combine_add(resid: torch.Tensor, mix: Optional[torch.Tensor], y: Optional[torch.Tensor], r: Optional[MoeRouting]) -> None:

@@ -298,6 +298,8 @@ class RoutedExperts(nn.Module):
     experts' outputs as compact rows (expert by expert) with the routing; `ops.moe_combine_add` sums them into the stream.
     Tensors under `prefix`: router, e<j>.gate, e<j>.up, e<j>.down."""
 
+    dense_rows_per_expert = 64   # average rows per expert from which a step runs one dense product per expert
+
     def __init__(self, prefix: str, weights, *, experts: int, top: int, limit: float, alpha: float = 1.702):
         super().__init__()
         _need_single_rank(weights, "RoutedExperts")
@@ -311,6 +313,22 @@ class RoutedExperts(nn.Module):
 
     def forward(self, h: torch.Tensor):
         routing = ops.moe_route(ops.linear(h, self.w_router, out_dtype=torch.float32), self.top)
+        rows = h.shape[0] * self.top
+        if h.dtype == torch.bfloat16 and rows >= self.dense_rows_per_expert * self.E and not torch.cuda.is_current_stream_capturing():
+            # prompts: enough rows per expert for the tcgen05 product (ops.linear) to pay - one product per expert over its run of
+            # compact rows; the runs' bounds are read back once per layer, so this form stays out of captured decode graphs
+            offs = ops.moe_expert_offsets(routing)
+            a = ops.moe_gather_rows(h, routing)
+            gu = torch.empty(rows, self.w_gate_up.shape[1], dtype=h.dtype, device=h.device)
+            for e in range(self.E):
+                if offs[e + 1] > offs[e]:
+                    ops.linear(a[offs[e]:offs[e + 1]], self.w_gate_up[e], out=gu[offs[e]:offs[e + 1]])
+            act = ops.ff_clamped_gate(gu, self.limit, self.alpha)
+            y = torch.empty(rows, self.w_down.shape[1], dtype=torch.float32, device=h.device)
+            for e in range(self.E):
+                if offs[e + 1] > offs[e]:
+                    ops.linear(act[offs[e]:offs[e + 1]], self.w_down[e], out=y[offs[e]:offs[e + 1]])
+            return y, routing
         gu = ops.moe_linear(h, self.w_gate_up, routing, gather=True, out_dtype=h.dtype)
         act = ops.ff_clamped_gate(gu, self.limit, self.alpha)
         return ops.moe_linear(act, self.w_down, routing, gather=False, out_dtype=torch.float32), routing

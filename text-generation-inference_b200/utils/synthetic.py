@@ -47,12 +47,34 @@ def fetotar_config(name: str) -> dict:
             "vocab": 32000, "width": W}
 
 
+def dubesun_config(name: str) -> dict:
+    """Three layers (distance-bias attention, differential attention, differential attention over the second layer's keys and
+    values), each with 16 routed experts of which a token uses 2, at the widths of the `neox-w*` partners: raw config.json of the
+    Dubesun family."""
+    W = {"dubesun-w2048": 2048, "dubesun-w4096": 4096}[name]
+    moe = {"kind": "moe", "expert": {"ff": W * 11 // 16, "limit": 7.0}, "router": {"experts": 16, "top": 2}}
+    diff = {"conv": 4, "diff": 0.8, "dim": 128, "heads": W // 256, "kv_heads": W // 1024, "q_temp": {"coef": 0.1, "every": 1024},
+            "scale": 128 ** -0.5, "vdim": 256}
+    layers = [
+        {"type": "attention_2", "mixer": {"bias_max": 4096, "dim": 128, "heads": W // 128, "kv_heads": W // 512, "scale": 128 ** -0.5, "vdim": 128},
+         "mlp": dict(moe)},
+        {"type": "attention", "mixer": dict(diff), "mlp": dict(moe)},
+        {"type": "attention", "mixer": dict(diff, kv_from=1), "mlp": dict(moe)},
+    ]
+    return {"architecture": "Dubesun", "layers": layers, "max_positions": 2048, "norm": {"eps": 1e-5}, "vocab": 32000, "width": W}
+
+
 class SyntheticHybridWeights:
-    """Seeded random tensors of a Fetotar configuration, generated on the device by name (the `get_tensor` side of `Weights`)."""
+    """Seeded random tensors of a Fetotar or Dubesun configuration, generated on the device by name (the `get_tensor` side of
+    `Weights`)."""
 
     def __init__(self, raw_config: dict, device, dtype, process_group, seed: int = 1234):
-        from ..models.custom_modeling.fetotar_modeling import tensor_shapes
+        if raw_config.get("architecture") == "Dubesun":
+            from ..models.custom_modeling.dubesun_modeling import tensor_shapes
+        else:
+            from ..models.custom_modeling.fetotar_modeling import tensor_shapes
         self.shapes, self.device, self.dtype, self.process_group, self.seed = tensor_shapes(raw_config), device, dtype, process_group, seed
+        self.offset_norms = raw_config.get("architecture") == "Dubesun"
 
     def get_tensor(self, name: str) -> torch.Tensor:
         shape = self.shapes[name]
@@ -65,8 +87,10 @@ class SyntheticHybridWeights:
             t = torch.rand(shape, generator=gen, device=self.device) * 2.0 - 2.0
         elif leaf == "mix.f.b":
             t = torch.full(shape, 3.0, device=self.device)
-        elif leaf.endswith(".b"):
-            t = torch.zeros(shape, device=self.device)
+        elif leaf.endswith(".b") or (self.offset_norms and (leaf == "norm1" or name == "final.norm")):
+            t = torch.zeros(shape, device=self.device)   # biases, and norm weights that are stored around zero
+        elif leaf in ("mix.lq1", "mix.lk1", "mix.lq2", "mix.lk2"):
+            t = torch.full(shape, 0.05, device=self.device)
         else:
             t = torch.ones(shape, device=self.device)
         return t.to(self.dtype)
