@@ -933,6 +933,147 @@ def run_hybrid_compare(args):
     return 0
 
 
+def run_dubesun_compare(args):
+    """Dubesun (bfloat16) beside GPT-NeoX (fp16) at equal width and depth, random weights: prefill of 4 x 1024 tokens and decode of
+    32 sequences at context 1024, measured as --hybrid-compare measures its pair: tokens/s through the engine's own step (device
+    time by CUDA events, L2 flushed between timed calls), device time per op family and per kernel of the graph-replayed decode
+    step, and for the kernels that carry a step the achieved FLOP/s or bytes/s against the measured peaks."""
+    import torch
+    import tgis_b200  # noqa: F401
+    from tgis_b200 import _lib as _libmod, ops_seq
+    from tgis_b200.inference_engine import InferenceEngine
+    from tgis_b200.models.custom_modeling.dubesun_modeling import DubesunConfig, tensor_shapes
+    from tgis_b200.models.flash_causal_lm import FlashCausalLM
+    from tgis_b200.utils.dist import FakeGroup
+    from tgis_b200.utils.synthetic import SyntheticHybridWeights, dubesun_config, make_tokenizer
+
+    pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        pk = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    PB, PL, DB, DL = 4, 1024, 32, 1024
+    K, Wm = max(args.steps // 4, 4), args.warmup
+    ctx = DL + Wm + K + 2
+    results = []
+
+    def timed(fn, n):
+        total = 0.0
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / n
+
+    widths = (2048, 4096) if not args.layers else (2048,)
+    for width in widths:
+        raw = dubesun_config(f"dubesun-w{width}")
+        cfg = DubesunConfig(raw)
+        weights = SyntheticHybridWeights(raw, dev, torch.bfloat16, FakeGroup(0, 1))
+        engine = InferenceEngine("<synthetic>", None, torch.bfloat16, None, cfg, None, weights=weights, tokenizer=make_tokenizer(cfg.vocab_size))
+        model = FlashCausalLM("<synthetic>", None, "tgis_native", torch.bfloat16, None, cfg, engine=engine,
+                              num_kv_blocks=(DB + PB) * ((DL + 64) // 16 + 2), num_state_slots=DB + PB)
+        g = torch.Generator().manual_seed(0)
+        prompt = lambda n, L: [torch.randint(4, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(n)]  # noqa: E731
+        prompts_p = prompt(PB, PL)
+
+        def prefill_once():
+            sids, _ = model.step_ragged([None] * PB, prompts_p, [PL * (i + 1) - 1 for i in range(PB)])
+            model.kv_cache_manager.free_sequences(sids)
+        for _ in range(Wm):
+            prefill_once()
+        pre_ms = timed(prefill_once, K)
+        names = ["linear", "embed_add_pos", "rmsnorm_rows", "causal_conv", "heads_prepare", "paged_attn", "diff_combine", "group_rmsnorm_gate",
+                 "moe_route", "moe_gather_rows", "moe_linear", "ff_clamped_gate", "moe_combine_add"]
+        log = []
+        saved = _timed_ops(ops_seq, names, log)
+        prefill_once()
+        pre_ops = _by_op(log)
+        for n, fn in saved.items():
+            setattr(ops_seq, n, fn)
+        sids, _ = model.step_ragged([None] * DB, prompt(DB, DL), [])
+        nxt = [[t[0]] for t in prompt(DB, 1)]   # a different token per sequence: the routing of the first layer sees only the token
+
+        def decode_once():
+            model.step_ragged(sids, nxt, None)
+        for _ in range(Wm):
+            decode_once()
+        dec_ms = timed(decode_once, K)
+        log, routes = [], []
+        route = ops_seq.moe_route
+        ops_seq.moe_route = lambda *a, **k: (routes.append(route(*a, **k)), routes[-1])[1]
+        saved = _timed_ops(ops_seq, names, log)
+        decode_once()
+        dec_ops = _by_op(log)
+        for n, fn in saved.items():
+            setattr(ops_seq, n, fn)
+        ops_seq.moe_route = route
+        picked = sum(len(set(r.ids.flatten().tolist())) for r in routes)   # experts whose weights a decode step reads, all layers
+        model.kv_cache_manager.free_sequences(sids)
+        # the serving path: from_pb -> generate_token, plain greedy, replayed as one CUDA graph from the third step of the batch
+        with torch.inference_mode():
+            gpb = make_batch_pb(DB, DL, Wm + K + 8)
+            for r, toks in zip(gpb.requests, prompt(DB, DL)):   # a prompt of its own per request: the routing differs between them
+                r.inputs = " ".join(f"<tok{t}>" for t in toks)
+            gbatch, _ = model.batch_type.from_pb(gpb, model.tokenizer, torch.bfloat16, model.device, None, None, True)
+            model.generate_token(gbatch, first=True)
+            for _ in range(Wm):
+                model.generate_token(gbatch)
+            graph_ms = timed(lambda: model.generate_token(gbatch), K)
+            dec_k, dec_total = _traced_decode_step(model, gbatch, _libmod.load_seq())
+            model.kv_cache_manager.free_sequences(gbatch.sequence_ids)
+        shapes = tensor_shapes(raw)
+        attn_flops, attn_rows = 0, 0
+        for layer in raw["layers"]:
+            m = layer["mixer"]
+            maps = 2 if layer["type"] == "attention" else 1
+            attn_flops += PB * (PL * (PL + 1) // 2) * m["heads"] * maps * (m["dim"] + m["vdim"]) * 2
+            attn_rows += m["kv_heads"] * (maps * m["dim"] + m["vdim"])   # elements a decoding token reads per cached token
+        f = raw["layers"][0]["mlp"]
+        E, top, ff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+        L = len(raw["layers"])
+        proj_w = sum(a * b for n, (a, *rest) in shapes.items() for b in rest[:1]
+                     if n.split(".")[-1] in ("q", "k", "v", "g", "o", "router") and ".mlp.e" not in n)
+        head_w = shapes["head"][0] * shapes["head"][1]
+        expert_w = 3 * width * ff
+        lin_flops = 2 * PB * PL * (proj_w + L * top * expert_w) + 2 * PB * head_w
+        attn_us = dec_k.get("paged_heads_attn_mma_kernel", 0.0) + dec_k.get("paged_heads_attn_merge_kernel", 0.0)
+        moe_us = dec_k.get("moe_linear_mma_kernel", 0.0)
+        kernels = {
+            "paged_attn prefill (3 layers)": {"ms": pre_ops["paged_attn"], "tflops": attn_flops / pre_ops["paged_attn"] / 1e9,
+                                              "of_measured_tensor": attn_flops / (pre_ops["paged_attn"] * 1e-3) / tens},
+            "paged_attn decode (3 layers)": {"us": attn_us, "of_measured_hbm": DB * ctx * attn_rows * 2 / (max(attn_us, 1e-9) * 1e-6) / hbm},
+            "linear prefill (projections + one product per expert)": {"ms": pre_ops["linear"], "of_measured_tensor": lin_flops / (pre_ops["linear"] * 1e-3) / tens},
+            "moe_linear decode (grouped, picked experts' weights once)": {"us": moe_us, "experts_picked_all_layers": picked, "of_measured_hbm":
+                                                                          picked * expert_w * 2 / (max(moe_us, 1e-9) * 1e-6) / hbm},
+            "linear decode (tcgen05 projections)": {"us": dec_k.get("gemm_f16_kernel", 0.0), "of_measured_hbm":
+                                                    (proj_w + head_w) * 2 / (max(dec_k.get("gemm_f16_kernel", 0.0), 1e-9) * 1e-6) / hbm},
+        }
+        results.append({"model": f"dubesun-w{width}", "dtype": "bf16", "layers": L, "experts": E, "top": top,
+                        "prefill_tokens_per_s": PB * PL / (pre_ms * 1e-3), "decode_tokens_per_s": DB / (dec_ms * 1e-3), "prefill_ms": pre_ms,
+                        "decode_ms_per_step": dec_ms, "decode_graph_tokens_per_s": DB / (graph_ms * 1e-3), "decode_graph_ms_per_step": graph_ms,
+                        "prefill_ms_by_op": {k: round(v, 4) for k, v in pre_ops.items()},
+                        "decode_ms_by_op": {k: round(v, 4) for k, v in dec_ops.items()},
+                        "decode_graph_us_by_kernel": {k: round(v, 2) for k, v in sorted(dec_k.items(), key=lambda kv: -kv[1])},
+                        "decode_graph_traced_us": dec_total, "kernels": kernels})
+        del model, engine, weights
+        gc.collect()
+        torch.cuda.empty_cache()
+        results.append(_neox_partner(width, PB, PL, DB, DL, K, Wm, timed, hbm, tens, ctx))
+    print(json.dumps({"metric": "dubesun_compare", "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": Wm, "data": "synthetic",
+                      "config": {"prefill": [PB, PL], "decode": [DB, DL], "l2": "flushed between timed calls"},
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk.get("source")}, "models": results}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -947,11 +1088,15 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the second workload, the self-check and the gpt2 CPU line")
     ap.add_argument("--hybrid-compare", action="store_true",
                     help="Fetotar beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
+    ap.add_argument("--dubesun-compare", action="store_true",
+                    help="Dubesun beside GPT-NeoX at equal size: prefill and decode throughput and per-kernel rooflines (one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.hybrid_compare:
         return run_hybrid_compare(args)
+    if args.dubesun_compare:
+        return run_dubesun_compare(args)
     workload = args.workload or DEFAULT_WORKLOAD
     if workload in MIXED_WORKLOADS:
         if args.impl == "reference":

@@ -91,7 +91,9 @@ int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int 
 int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,
                         int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B, const int64_t* position_ids, float* out,
                         int64_t Tq, int H, int G, int maps, int d, int dv, int window, float scale, int page, const float* rel,
-                        const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, void* stream);
+                        const int32_t* bucket_tab, int n_bucket_tab, int rel_rows, float* partial, int nsplit, void* stream);
+/* blocks to split each query tile's keys over for this step (0: plain kernel, 1: no split) and the fp32 workspace for `partial` */
+int b200_seq_paged_attn_splits(int dt, int64_t Tq, int B, int H, int G, int maps, int d, int dv, int64_t* workspace_floats);
 /* in fp32 [T, H, 2, dv] -> out [T, H * dv]: (a1 - lambda a2) / sqrt(mean(.^2) + eps) * out_scale */
 int b200_seq_diff_combine(const float* in, void* out, int out_dt, int64_t T, int H, int dv, float lambda, float out_scale, float eps,
                           void* stream);

@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
     int64_t bt_stride, const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ out, int B, int H, int rep,
     int maps, int d, int window, float scale, int page, const float* __restrict__ rel, const int32_t* __restrict__ bucket_tab, int n_bucket_tab,
-    int rel_rows) {
+    int rel_rows, float* __restrict__ partial) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int dv = NDV * 8, VP = dv + kMmaPad;
@@ -210,35 +210,47 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     if (tile < nt) break;
     tile -= nt;
   }
-  if (b >= B) return;
+  if (b >= B) return;  // block-uniform: no barrier has been met yet
   const int g = blockIdx.y;
   const int row0 = cu_q[b] + tile * QT;
   const int ntok = min(QT, cu_q[b + 1] - row0);
   const int p0 = (int)position_ids[row0], p_last = p0 + ntok - 1;
-  const int j_start = max(0, p0 - window + 1);
+  // gridDim.z > 1: the tile's key tiles are dealt out in contiguous runs to gridDim.z blocks, whose (unnormalised output, max, sum)
+  // per row are merged by paged_heads_attn_merge_kernel; a block whose run is empty records an empty partial
+  const int j_first = max(0, p0 - window + 1);
+  const int n_ktiles = (p_last - j_first + KT) / KT;
+  const int per_split = (n_ktiles + gridDim.z - 1) / gridDim.z;
+  const int j_start = j_first + (int)blockIdx.z * per_split * KT;
+  const int j_end = min(p_last, j_start + per_split * KT - 1);   // last key of this block's run
   const int w = warp_id(), lane = lane_id();
   const int Hq = H * maps;
   const int32_t* table = block_table + (int64_t)b * bt_stride;
-  for (int idx = threadIdx.x; idx < kMmaRows * d; idx += kMmaThreads) {
-    const int r = idx / d, c = idx % d;
+  for (int r = w; r < kMmaRows; r += kMmaThreads / 32) {  // one division set per row, not per element
     const int mp = r / rpm, rr = r % rpm, tok = rr / rep, hh = rr % rep;
-    float v = 0.f;
-    if (tok < ntok) v = q[((int64_t)(row0 + tok) * Hq + (g * rep + hh) * maps + mp) * d + c] * scale;
-    Qs[r * DP + c] = __float2bfloat16_rn(v);
+    const float* src = q + ((int64_t)(row0 + tok) * Hq + (g * rep + hh) * maps + mp) * d;
+    const bool live = tok < ntok;
+    for (int c = lane; c < d; c += 32) Qs[r * DP + c] = __float2bfloat16_rn(live ? src[c] * scale : 0.f);
   }
   const int kchunks = KD / 8, vchunks = dv / 8, cpr = kchunks + vchunks;
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+  // eight threads per key row: one block-table lookup per thread and row, then the row's 16-byte pieces go round the eight
   auto load_tile = [&](int stage, int j0) {
     __nv_bfloat16* kd = Ks + stage * KT * KP;
     __nv_bfloat16* vd = Vs + stage * KT * VP;
-    for (int idx = threadIdx.x; idx < KT * cpr; idx += kMmaThreads) {
-      const int row = idx / cpr, ch = idx % cpr, j = j0 + row;
-      __nv_bfloat16* dst = ch < kchunks ? kd + row * KP + ch * 8 : vd + row * VP + (ch - kchunks) * 8;
-      if (j <= p_last) {
-        const __nv_bfloat16* src = cache + ((int64_t)table[j / page] * page + j % page) * RW;
-        src += ch < kchunks ? k_off + (int64_t)g * KD + ch * 8 : v_off + (int64_t)g * dv + (ch - kchunks) * 8;
-        cp_async_16(dst, src, true);
+    for (int row = threadIdx.x >> 3; row < KT; row += kMmaThreads / 8) {
+      const int j = j0 + row;
+      __nv_bfloat16* krow = kd + row * KP;
+      __nv_bfloat16* vrow = vd + row * VP;
+      if (j <= j_end) {
+        const int64_t crow = page_shift >= 0 ? ((int64_t)table[j >> page_shift] << page_shift) + (j & (page - 1))
+                                             : (int64_t)table[j / page] * page + j % page;
+        const __nv_bfloat16* ksrc = cache + crow * RW + k_off + (int64_t)g * KD;
+        const __nv_bfloat16* vsrc = cache + crow * RW + v_off + (int64_t)g * dv;
+        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, ksrc + ch * 8, true);
+        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, vsrc + ch * 8, true);
       } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);  // finite: these rows meet p = 0
+        for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(krow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+        for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) *reinterpret_cast<uint4*>(vrow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: p = 0
       }
     }
     cp_async_commit();
@@ -264,9 +276,9 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
   const int lm = lane >> 3, lr = lane & 7;
   const uint32_t a_lane = qs_addr + (uint32_t)(((w * 16 + (lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
   int stage = 0;
-  load_tile(0, j_start);
-  for (int j0 = j_start; j0 <= p_last; j0 += KT, stage ^= 1) {
-    if (j0 + KT <= p_last) {
+  if (j_start <= j_end) load_tile(0, j_start);
+  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage ^= 1) {
+    if (j0 + KT <= j_end) {
       load_tile(stage ^ 1, j0 + KT);
       cp_async_wait<1>();
     } else {
@@ -297,7 +309,7 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
           const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
           const int dist = p_row[i] - j;
           float v = s[nt][e];
-          if (dist < 0 || dist >= window) {
+          if (dist < 0 || dist >= window || j > j_end) {
             v = -INFINITY;
           } else if (rel) {
             v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
@@ -353,6 +365,25 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     }
     __syncthreads();  // everyone is done with this stage before the load after next overwrites it
   }
+  if (gridDim.z > 1) {
+    // partial [tile][g][split][64 rows][dv + 2]: unnormalised output, then the running max and sum
+    float* base = partial + ((((int64_t)blockIdx.x * gridDim.y + g) * gridDim.z + blockIdx.z) * kMmaRows) * (dv + 2);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!valid[i]) continue;
+      float* dst = base + (int64_t)(w * 16 + (lane >> 2) + i * 8) * (dv + 2);
+#pragma unroll
+      for (int nt = 0; nt < NDV; ++nt) {
+        dst[nt * 8 + cq] = o[nt][i * 2];
+        dst[nt * 8 + cq + 1] = o[nt][i * 2 + 1];
+      }
+      if ((lane & 3) == 0) {
+        dst[dv] = m_run[i];
+        dst[dv + 1] = l_run[i];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (!valid[i]) continue;
@@ -364,6 +395,55 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     for (int nt = 0; nt < NDV; ++nt) {
       dst[nt * 8 + cq] = o[nt][i * 2] * inv;
       dst[nt * 8 + cq + 1] = o[nt][i * 2 + 1] * inv;
+    }
+  }
+}
+
+// out[row] = sum_z e^(m_z - M) O_z / sum_z e^(m_z - M) l_z over the key splits of paged_heads_attn_mma_kernel; one block per
+// (query tile, key/value head), one warp per row
+__global__ void __launch_bounds__(256) paged_heads_attn_merge_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                                    const int32_t* __restrict__ cu_q, int B, int H, int rep, int maps, int dv,
+                                                                    int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rpm = kMmaRows / maps, QT = rpm / rep;
+  int tile = blockIdx.x, b = 0;
+  for (; b < B; ++b) {
+    const int nt = (cu_q[b + 1] - cu_q[b] + QT - 1) / QT;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (b >= B) return;
+  const int g = blockIdx.y, lane = lane_id();
+  const int row0 = cu_q[b] + tile * QT;
+  const int ntok = min(QT, cu_q[b + 1] - row0);
+  const int Hq = H * maps;
+  constexpr int kMaxSplit = 8;
+  for (int r = warp_id(); r < kMmaRows; r += 8) {
+    const int rr = r % rpm, tok = rr / rep;
+    if (tok >= ntok) continue;
+    const float* base = partial + ((((int64_t)blockIdx.x * gridDim.y + g) * nsplit) * kMmaRows + r) * (dv + 2);
+    const int64_t zs = (int64_t)kMmaRows * (dv + 2);
+    float M = -INFINITY, wz[kMaxSplit];
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = z < nsplit ? base[z * zs + dv] : -INFINITY;
+      M = fmaxf(M, wz[z]);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = wz[z] > -INFINITY ? expf(wz[z] - M) : 0.f;  // an empty run carries no weight
+      if (z < nsplit) den += wz[z] * base[z * zs + dv + 1];
+    }
+    const float inv = 1.f / den;
+    float* dst = out + ((int64_t)(row0 + tok) * Hq + (g * rep + rr % rep) * maps + r / rpm) * dv;
+    for (int c = lane; c < dv; c += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int z = 0; z < kMaxSplit; ++z)
+        if (z < nsplit) acc = fmaf(wz[z], base[z * zs + c], acc);
+      dst[c] = acc * inv;
     }
   }
 }
@@ -427,16 +507,38 @@ static int launch_paged_heads_attn(const float* q, const void* cache, int64_t RW
   return B200_OK;
 }
 
+static bool attn_mma_shape_ok(int dt, int H, int G, int maps, int d, int dv) {
+  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_ATTN_MMA"); return !(e && e[0] == '0'); }();
+  return use_mma && dt == B200_DT_BF16 && G > 0 && H % G == 0 && maps >= 1 && maps <= 2 && kMmaRows % ((H / G) * maps) == 0 && d % 16 == 0 &&
+         dv % 16 == 0 && dv <= 256;
+}
+
+// Over how many blocks the tensor-core kernel should split every query tile's keys for this step (1: no split; 0: the shape takes
+// the plain kernel) and the fp32 workspace (`partial`) that takes: steps with few query rows (decoding) leave most SMs idle with one
+// block per (query tile, key/value head).
+extern "C" int b200_seq_paged_attn_splits(int dt, int64_t Tq, int B, int H, int G, int maps, int d, int dv, int64_t* workspace_floats) {
+  if (workspace_floats) *workspace_floats = 0;
+  if (!attn_mma_shape_ok(dt, H, G, maps, d, dv)) return 0;
+  const int QT = kMmaRows / ((H / G) * maps);
+  const int64_t tiles = (Tq + QT - 1) / QT + B;
+  const int64_t busy = ((Tq + QT - 1) / QT > B ? (Tq + QT - 1) / QT : B) * G;   // blocks that have rows: between the two bounds
+  int64_t n = (2 * 148) / (busy > 0 ? busy : 1);
+  n = n < 1 ? 1 : (n > 8 ? 8 : n);
+  if (n > 1 && workspace_floats) *workspace_floats = tiles * G * n * kMmaRows * (dv + 2);
+  return (int)n;
+}
+
 // q fp32 [Tq, H * maps, d] (query head h, map m at index h * maps + m); cache [blocks, page, row_width] of type dt with G * maps key
 // heads of d elements from k_off (key head g, map m at g * maps + m) and G value heads of dv elements from v_off; out fp32
 // [Tq, H * maps, dv].  window <= 0: every earlier token is visible.  rel (fp32 [rel_rows, H]) NULL: no bias; otherwise
 // rel[bucket(distance), h] is added to the scaled score, bucket(n) = bucket_tab[n] for n < n_bucket_tab and rel_rows - 1 beyond.
 // cu_q [B + 1]: row boundaries of the step's sequences (the tensor-core kernel tiles a sequence's rows; NULL: plain kernel only).
+// `partial` / nsplit: from b200_seq_paged_attn_splits (NULL / <= 1: no split).
 extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off,
                                    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_of_token, const int32_t* cu_q, int B,
                                    const int64_t* position_ids, float* out, int64_t Tq, int H, int G, int maps, int d, int dv, int window,
                                    float scale, int page, const float* rel, const int32_t* bucket_tab, int n_bucket_tab, int rel_rows,
-                                   void* stream) {
+                                   float* partial, int nsplit, void* stream) {
   if (Tq == 0) return B200_OK;
   if (G <= 0 || H % G != 0 || maps < 1 || d <= 0 || dv <= 0 || dv > 512) {
     b200_set_last_error("seq_paged_attn: need heads % kv_heads == 0, maps >= 1, 0 < vdim <= 512");
@@ -445,23 +547,27 @@ extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, in
   if (window <= 0) window = 0x3fffffff;
   cudaStream_t st = (cudaStream_t)stream;
   const int rows_g = (H / G) * maps;
-  static const bool use_mma = []() { const char* e = getenv("B200_SEQ_ATTN_MMA"); return !(e && e[0] == '0'); }();
-  if (use_mma && dt == B200_DT_BF16 && cu_q != nullptr && maps <= 2 && kMmaRows % rows_g == 0 && d % 16 == 0 && dv % 16 == 0 && dv <= 256 &&
-      row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+  if (attn_mma_shape_ok(dt, H, G, maps, d, dv) && cu_q != nullptr && row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
     const int QT = kMmaRows / rows_g;
     const int64_t tiles = (Tq + QT - 1) / QT + B;  // upper bound of sum_b ceil(n_b / QT); surplus blocks return at once
     const int kt = dv <= 128 ? 64 : 32;
     const size_t smem = ((size_t)kMmaRows * (d + kMmaPad) + 2 * (size_t)kt * (maps * d + kMmaPad) + 2 * (size_t)kt * (dv + kMmaPad)) * 2;
     if (smem <= 200 * 1024 && tiles <= 0x7fffffff) {
-      dim3 grid((unsigned)tiles, (unsigned)G);
+      if (!partial || nsplit < 1) nsplit = 1;
+      if (nsplit > 8) nsplit = 8;
+      dim3 grid((unsigned)tiles, (unsigned)G, (unsigned)nsplit);
 #define PAM(N, KT)                                                                                                                       \
   do {                                                                                                                                   \
     static bool cfg = false;                                                                                                             \
     if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_mma_kernel<N, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
     B200_LAUNCH((paged_heads_attn_mma_kernel<N, KT>), grid, dim3(kMmaThreads), smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
                 block_table, bt_stride, cu_q, position_ids, out, B, H, H / G, maps, d, window, scale, page, rel, bucket_tab, n_bucket_tab,  \
-                rel_rows);                                                                                                               \
-    b200_count_launches(1);                                                                                                              \
+                rel_rows, partial);                                                                                                      \
+    if (nsplit > 1)                                                                                                                      \
+      B200_LAUNCH(paged_heads_attn_merge_kernel, dim3((unsigned)tiles, (unsigned)G), dim3(256), 0, st, (const float*)partial, out, cu_q, B, H, \
+                  H / G, maps, dv, nsplit);                                                                                              \
+    b200_count_launches(nsplit > 1 ? 2 : 1);                                                                                             \
     return B200_OK;                                                                                                                      \
   } while (0)
       switch (dv / 8) {

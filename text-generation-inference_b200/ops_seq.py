@@ -318,12 +318,16 @@ def paged_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, heads:
     assert Hq == heads * maps and q.is_contiguous() and cache.is_contiguous() and q.dtype == torch.float32
     assert rel is None or (rel.dtype == torch.float32 and rel.is_contiguous() and rel.shape[1] == heads and bucket_tab.dtype == torch.int32)
     out = torch.empty(T, Hq, vdim, dtype=torch.float32, device=q.device)
-    _lib.check_seq(_lib.load_seq().b200_seq_paged_attn(
+    lib = _lib.load_seq()
+    need = ctypes.c_int64(0)
+    nsplit = lib.b200_seq_paged_attn_splits(_dt(cache), T, step.B, heads, kv_heads, maps, d, vdim, ctypes.byref(need)) if _ATTN_SPLIT else 1
+    partial = torch.empty(need.value, dtype=torch.float32, device=q.device) if nsplit > 1 else None
+    _lib.check_seq(lib.b200_seq_paged_attn(
         _ptr(q), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off, _ptr(step.block_table), step.block_table.stride(0),
         _ptr(step.seq_of_token), _ptr(step.cu_q), step.B, _ptr(step.position_ids), _ptr(out), T, heads, kv_heads, maps, d, vdim, int(window),
         float(scale),
         cache.shape[1], _ptr(rel), _ptr(bucket_tab), 0 if bucket_tab is None else bucket_tab.shape[0], 0 if rel is None else rel.shape[0],
-        _stream()), "seq_paged_attn")
+        _ptr(partial), nsplit, _stream()), "seq_paged_attn")
     return out
 
 
