@@ -1045,7 +1045,7 @@ def run_dubesun_compare(args):
         head_w = shapes["head"][0] * shapes["head"][1]
         expert_w = 3 * width * ff
         lin_flops = 2 * PB * PL * (proj_w + L * top * expert_w) + 2 * PB * head_w
-        attn_us = dec_k.get("paged_heads_attn_mma_kernel", 0.0) + dec_k.get("paged_heads_attn_merge_kernel", 0.0)
+        attn_us = sum(v for k, v in dec_k.items() if k.startswith("paged_heads_attn"))   # the attention kernel of the step and its merge
         moe_us = dec_k.get("moe_linear_mma_kernel", 0.0)
         kernels = {
             "paged_attn prefill (3 layers)": {"ms": pre_ops["paged_attn"], "tflops": attn_flops / pre_ops["paged_attn"] / 1e9,

@@ -108,11 +108,14 @@ def biased_attention(h, p, m: dict, eps: float):
     return (o * torch.sigmoid(h @ p["g"].T)) @ p["o"].T
 
 
-def moe(h, p, f: dict):
-    """h [L, W] -> [L, W]: the `top` experts with the largest router logits, weighted by the soft-max over those logits"""
+def moe(h, p, f: dict, margins: Optional[list] = None):
+    """h [L, W] -> [L, W]: the `top` experts with the largest router logits, weighted by the soft-max over those logits.
+    `margins`, when a list, receives per row the gap between the last picked logit and the best one left out (inf when all are picked)"""
     E, top, limit = int(f["router"]["experts"]), int(f["router"]["top"]), float(f["expert"]["limit"])
     z = h @ p["router"].T
     val, idx = torch.topk(z, top, dim=-1)
+    if margins is not None:
+        margins.append(val[:, -1] - torch.topk(z, top + 1, dim=-1).values[:, -1] if top < E else torch.full_like(val[:, 0], float("inf")))
     wgt = torch.softmax(val, -1)
     out = torch.zeros(h.shape[0], p["e0.down"].shape[0], dtype=h.dtype)
     for e in range(E):
@@ -124,8 +127,10 @@ def moe(h, p, f: dict):
 
 
 # ------------------------------------------------------------------------------------------------ the model
-def forward(config: dict, sd: Dict[str, torch.Tensor], tokens: List[int], dtype=F64, residuals: Optional[list] = None):
-    """logits [L, vocab] of one sequence; `residuals`, when a list, receives the stream after every layer"""
+def forward(config: dict, sd: Dict[str, torch.Tensor], tokens: List[int], dtype=F64, residuals: Optional[list] = None,
+            margins: Optional[list] = None):
+    """logits [L, vocab] of one sequence; `residuals`, when a list, receives the stream after every layer, `margins` the routing
+    margin of every position in every routed layer (a reduced-precision run may pick other experts where it is small)"""
     sd = {k: v.to(dtype) for k, v in sd.items()}
     eps = float(config["norm"]["eps"])
     ids = torch.tensor(tokens, dtype=torch.int64)
@@ -145,7 +150,7 @@ def forward(config: dict, sd: Dict[str, torch.Tensor], tokens: List[int], dtype=
         else:
             raise NotImplementedError(layer["type"])
         if layer.get("mlp"):
-            y = y + moe(n, sub(sd, f"l{i}.mlp."), layer["mlp"])
+            y = y + moe(n, sub(sd, f"l{i}.mlp."), layer["mlp"], margins)
         x = x + y
         if residuals is not None:
             residuals.append(x.clone())

@@ -51,6 +51,13 @@ def _rel(got, ref):
     return float(((got - ref).pow(2).mean(-1).sqrt() / ref.std()).max())
 
 
+def _decided(config, sd, tokens, least=0.1):
+    """positions whose routing is no close call in any layer: where bfloat16 must pick the reference's experts"""
+    margins = []
+    orc.forward(config, sd, tokens, margins=margins)
+    return torch.stack(margins).min(0).values > least
+
+
 def _run_cut(model, tokens, cuts):
     """one sequence in portions of the given sizes (the rest token by token) -> logits of every position"""
     sid, at, rows = None, 0, []
@@ -202,6 +209,11 @@ MIXER_CASES = [
     ("attention", {"conv": 2, "diff": 0.3, "dim": 32, "heads": 2, "kv_heads": 2, "q_temp": {"coef": 0.2, "every": 3}, "scale": 0.3, "vdim": 144}),
     ("attention_2", {"bias_max": 40, "dim": 32, "heads": 8, "kv_heads": 2, "scale": 0.4, "vdim": 32, "rel_rows": 12}),
     ("attention_2", {"bias_max": 25, "dim": 16, "heads": 16, "kv_heads": 1, "scale": 0.4, "vdim": 16, "rel_rows": 10}),
+    # ... and, with value sizes in 64s and a head group of at most 16 rows, its decode form for steps of few rows
+    ("attention", {"conv": 3, "diff": 0.55, "dim": 16, "heads": 4, "kv_heads": 2, "q_temp": {"coef": 0.4, "every": 7}, "scale": 0.5, "vdim": 64}),
+    ("attention", {"conv": 2, "diff": 0.4, "dim": 32, "heads": 8, "kv_heads": 1, "q_temp": {"coef": 0.3, "every": 5}, "scale": 0.3, "vdim": 128}),
+    ("attention_2", {"bias_max": 40, "dim": 64, "heads": 6, "kv_heads": 2, "scale": 0.3, "vdim": 64, "rel_rows": 12}),
+    ("attention_2", {"bias_max": 30, "dim": 64, "heads": 16, "kv_heads": 1, "scale": 0.3, "vdim": 64, "rel_rows": 8}),
 ]
 
 
@@ -262,7 +274,8 @@ def _attn_reference(q, krows, vrows, q_pos, H, G, maps, scale, rel=None, rows=0,
 
 
 @pytest.mark.parametrize("maps,H,G,d,dv", [(2, 4, 2, 12, 20), (1, 6, 2, 10, 10), (2, 5, 1, 8, 40), (2, 4, 2, 16, 48), (1, 8, 2, 32, 32),
-                                          (2, 2, 1, 16, 160), (1, 64, 1, 16, 16)])
+                                          (2, 2, 1, 16, 160), (1, 64, 1, 16, 16), (2, 4, 2, 16, 64), (1, 16, 1, 32, 128), (2, 8, 1, 16, 64),
+                                          (1, 3, 1, 16, 64), (2, 3, 1, 32, 256)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_paged_attention_far_keys_page_borders_first_tokens(dtype, maps, H, G, d, dv):
     """one key per query is made to dominate the soft-max of one map; it sits hundreds of tokens back, on either side of a page
@@ -304,7 +317,7 @@ def test_paged_attention_far_keys_page_borders_first_tokens(dtype, maps, H, G, d
         assert torch.allclose(got[p], ref[i], atol=tol), ("prompt", pairs[i])
 
 
-@pytest.mark.parametrize("dtype,d", [(torch.float32, 8), (torch.bfloat16, 16)])
+@pytest.mark.parametrize("dtype,d", [(torch.float32, 8), (torch.bfloat16, 16), (torch.bfloat16, 64)])
 @pytest.mark.parametrize("rows,far", [(12, 40.0), (32, 200.0), (4, 9.0)])
 def test_distance_bias_bucket_edges(rows, far, dtype, d):
     """one row of the bias table is loud: the keys of that bucket take the whole soft-max, so a key counted into the neighbouring
@@ -362,8 +375,10 @@ def test_prompt_portions_and_decoding_agree_with_reference(tmp_path, dtype):
     toks = _tokens(2, 75, cfg["vocab"])
     ref = orc.forward(cfg, sd, toks)
     tol = TOL32 if dtype == torch.float32 else TOL16
+    sure = _decided(cfg, sd, toks) if dtype == torch.bfloat16 else torch.ones(75, dtype=torch.bool)
+    assert int(sure.sum()) > 50
     whole = _run_cut(model, toks, [75])
-    assert _rel(whole, ref) < tol
+    assert _rel(whole[sure], ref[sure]) < tol
     # the mechanisms are live in this configuration: a reference without the shared keys, with another temperature period or
     # with another far distance of the buckets is far outside the tolerance
     for path, wrong in ((("layers", 2, "mixer", "kv_from"), 3), (("layers", 0, "mixer", "q_temp", "every"), 8),
@@ -383,7 +398,7 @@ def test_prompt_portions_and_decoding_agree_with_reference(tmp_path, dtype):
             assert _rel(orc.forward(c2, sd, toks), ref) > 20 * TOL32, path
     for cuts in ([], [40], [2, 2, 2, 19, 3, 16, 17, 2], [16, 16, 16, 16], [7, 7, 7, 7, 7], [1, 20, 22, 31]):
         got = _run_cut(model, toks, cuts)
-        assert _rel(got, ref) < tol, cuts
+        assert _rel(got[sure], ref[sure]) < tol, cuts
         if dtype == torch.float32:
             assert _rel(got, whole.cpu()) < 1e-5, cuts  # the cut itself changes nothing beyond rounding
     assert model.kv_cache_manager.free_blocks == model.kv_cache_manager.total_num_gpu_blocks
@@ -394,20 +409,22 @@ def test_tensor_core_shapes_through_the_engine(tmp_path):
     """bfloat16 with head sizes in 16s: prompts, portions and decoded tokens take the tensor-core attention kernel; a step mixes
     a long portion (several query tiles) with single tokens"""
     cfg = _sharp(orc.random_config(width=64, order=("attention", "attention_2", "attention"), kv_from=(None, None, 0), heads=(8, 4),
-                                   kv_heads=(2, 2), dim=(16, 16), vdim=32, max_positions=256), 3.0)
+                                   kv_heads=(2, 2), dim=(16, 16), vdim=64, max_positions=256), 3.0)
     sd = orc.random_state_dict(cfg, seed=12)
     model = _model(tmp_path, cfg, sd, torch.bfloat16)
     toks = _tokens(3, 150, cfg["vocab"])
-    ref = orc.forward(cfg, sd, toks)
+    ref, sure = orc.forward(cfg, sd, toks), _decided(cfg, sd, toks)
+    assert int(sure.sum()) > 100
     for cuts in ([150], [100, 2, 40], [1, 70, 33], [5]):
-        assert _rel(_run_cut(model, toks, cuts), ref) < TOL16, cuts
+        assert _rel(_run_cut(model, toks, cuts)[sure], ref[sure]) < TOL16, cuts
     other = _tokens(4, 90, cfg["vocab"])
-    ref_o = orc.forward(cfg, sd, other)
+    ref_o, sure_o = orc.forward(cfg, sd, other), _decided(cfg, sd, other)
     (a,), la = model.step_ragged([None], [toks[:20]])
     (a, b), l2 = model.step_ragged([a, None], [toks[20:21], other[:80]])
     (b, a), l3 = model.step_ragged([b, a], [other[80:], toks[21:150]])
     model.kv_cache_manager.free_sequences([a, b])
-    assert _rel(torch.cat([la, l2[:1], l3[10:]]), ref) < TOL16 and _rel(torch.cat([l2[1:], l3[:10]]), ref_o) < TOL16
+    assert _rel(torch.cat([la, l2[:1], l3[10:]])[sure], ref[sure]) < TOL16
+    assert _rel(torch.cat([l2[1:], l3[:10]])[sure_o], ref_o[sure_o]) < TOL16
 
 
 def test_residual_stream_after_every_layer(tmp_path):

@@ -12,6 +12,7 @@
 //                          and decoded tokens are the same case: every key is read back from the cache.
 //   paged_heads_attn_mma_kernel : the same on bfloat16 caches with m16n8k16 tensor-core products; one block per (sequence, key/value
 //                          head, tile of query tokens), rows = (map, token, query head of the group); see the note above the kernel.
+//   paged_heads_attn_dec_kernel : decode form of the tensor-core kernel for steps of few rows (see the note above the kernel).
 //   diff_combine_kernel  : o = a1 - lambda a2 per head, o / sqrt(mean(o^2) + eps) * out_scale.
 #include "seq_common.cuh"
 
@@ -187,7 +188,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NDV, int KT>  // NDV = vdim / 8 output n-tiles per warp, KT keys per tile
+template <int NDV, int KT, int STAGES>  // NDV = vdim / 8 output n-tiles per warp, KT keys per tile, STAGES tile buffers
 __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
     int64_t bt_stride, const int32_t* __restrict__ cu_q, const int64_t* __restrict__ position_ids, float* __restrict__ out, int B, int H, int rep,
@@ -199,8 +200,8 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int KD = maps * d, KP = KD + kMmaPad, DP = d + kMmaPad;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][DP]
-  __nv_bfloat16* Ks = Qs + kMmaRows * DP;                            // [2][KT][KP]
-  __nv_bfloat16* Vs = Ks + 2 * KT * KP;                              // [2][KT][VP]
+  __nv_bfloat16* Ks = Qs + kMmaRows * DP;                            // [STAGES][KT][KP]
+  __nv_bfloat16* Vs = Ks + STAGES * KT * KP;                         // [STAGES][KT][VP]
   const int rpm = kMmaRows / maps;   // rows per map
   const int QT = rpm / rep;          // query tokens per tile
   // which (sequence, tile of its tokens) this block has
@@ -275,14 +276,20 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
   const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
   const int lm = lane >> 3, lr = lane & 7;
   const uint32_t a_lane = qs_addr + (uint32_t)(((w * 16 + (lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
+  // STAGES - 1 tiles are in flight ahead of the one being used; every iteration commits one group (an empty one past the end),
+  // so "at most STAGES - 1 groups pending" always means that the current tile has landed
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (j_start + st * KT <= j_end) load_tile(st, j_start + st * KT);
+    else cp_async_commit();
+  }
   int stage = 0;
-  if (j_start <= j_end) load_tile(0, j_start);
-  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage ^= 1) {
-    if (j0 + KT <= j_end) {
-      load_tile(stage ^ 1, j0 + KT);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+    {
+      const int jn = j0 + (STAGES - 1) * KT;
+      if (jn <= j_end) load_tile(stage == 0 ? STAGES - 1 : stage - 1, jn);
+      else cp_async_commit();
+      cp_async_wait<STAGES - 1>();
     }
     __syncthreads();  // the tile (and, first time round, Qs) is in shared memory
     if (warp_active) {
@@ -363,7 +370,7 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
         }
       }
     }
-    __syncthreads();  // everyone is done with this stage before the load after next overwrites it
+    __syncthreads();  // everyone is done with this stage before the next iteration's load overwrites it
   }
   if (gridDim.z > 1) {
     // partial [tile][g][split][64 rows][dv + 2]: unnormalised output, then the running max and sum
@@ -448,6 +455,234 @@ __global__ void __launch_bounds__(256) paged_heads_attn_merge_kernel(const float
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// Decode form of the tensor-core kernel, for steps of few query rows.  One block of four warps per (query token, key/value head,
+// run of the token's keys): the token's rows of that head group - (rep query heads) x maps, at most 16 - are ONE m16 tile; rows
+// 0..7 carry map 1 and rows 8..15 map 2 when there are two maps.  Every warp scores the whole 16-key tile (the same S in all four:
+// a few MMAs) and keeps the same running max and sum, but accumulates only its quarter of the value columns, so a thread holds
+// vdim / 16 output values instead of vdim / 2 and several blocks share an SM, each with STAGES - 1 small tiles in flight: the
+// key / value stream of a decoding step is bound by memory latency, not by work.  Partials per run are merged by
+// paged_heads_attn_dec_merge_kernel.  Needs dim % 16 == 0, vdim % 64 == 0, rep * maps <= 16 (rep <= 8 with two maps).
+// ------------------------------------------------------------------------------------------------------------------------
+constexpr int kDecKT = 16, kDecStages = 4, kDecRows = 16;
+
+template <int NDVW>  // n-tiles (8 value columns each) per warp: vdim = 32 * NDVW
+__global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
+    const float* __restrict__ q, const __nv_bfloat16* __restrict__ cache, int64_t RW, int k_off, int v_off, const int32_t* __restrict__ block_table,
+    int64_t bt_stride, const int32_t* __restrict__ seq_of_token, const int64_t* __restrict__ position_ids, float* __restrict__ out, int H, int rep,
+    int maps, int d, int window, float scale, int page, const float* __restrict__ rel, const int32_t* __restrict__ bucket_tab, int n_bucket_tab,
+    int rel_rows, float* __restrict__ partial) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int dv = NDVW * 32, VP = dv + kMmaPad, KT = kDecKT, STAGES = kDecStages;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int KD = maps * d, KP = KD + kMmaPad, DP = d + kMmaPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][DP]
+  __nv_bfloat16* Ks = Qs + kDecRows * DP;                            // [STAGES][KT][KP]
+  __nv_bfloat16* Vs = Ks + STAGES * KT * KP;                         // [STAGES][KT][VP]
+  const int64_t t = blockIdx.x;
+  const int g = blockIdx.y;
+  const int b = seq_of_token[t];
+  const int p = (int)position_ids[t];
+  const int j_first = max(0, p - window + 1);
+  const int n_ktiles = (p - j_first + KT) / KT;
+  const int per_split = (n_ktiles + gridDim.z - 1) / gridDim.z;
+  const int j_start = j_first + (int)blockIdx.z * per_split * KT;
+  const int j_end = min(p, j_start + per_split * KT - 1);
+  const int w = warp_id(), lane = lane_id();
+  const int Hq = H * maps;
+  const int32_t* table = block_table + (int64_t)b * bt_stride;
+  // row r of the tile: two maps -> map r / 8, head r % 8 of the group; one map -> head r
+  for (int r = w; r < kDecRows; r += kMmaThreads / 32) {
+    const int mp = maps == 2 ? r >> 3 : 0, hh = maps == 2 ? r & 7 : r;
+    const bool live = hh < rep;
+    const float* src = q + ((int64_t)t * Hq + (g * rep + (live ? hh : 0)) * maps + mp) * d;
+    for (int c = lane; c < d; c += 32) Qs[r * DP + c] = __float2bfloat16_rn(live ? src[c] * scale : 0.f);
+  }
+  const int kchunks = KD / 8, vchunks = dv / 8;
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+  auto load_tile = [&](int stage, int j0) {  // eight threads per key row, sixteen rows: one pass
+    const int row = threadIdx.x >> 3, j = j0 + row;
+    __nv_bfloat16* krow = Ks + (stage * KT + row) * KP;
+    __nv_bfloat16* vrow = Vs + (stage * KT + row) * VP;
+    if (j <= j_end) {
+      const int64_t crow = page_shift >= 0 ? ((int64_t)table[j >> page_shift] << page_shift) + (j & (page - 1))
+                                           : (int64_t)table[j / page] * page + j % page;
+      const __nv_bfloat16* ksrc = cache + crow * RW + k_off + (int64_t)g * KD;
+      const __nv_bfloat16* vsrc = cache + crow * RW + v_off + (int64_t)g * dv;
+      for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, ksrc + ch * 8, true);
+      for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, vsrc + ch * 8, true);
+    } else {
+      for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) *reinterpret_cast<uint4*>(krow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+      for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) *reinterpret_cast<uint4*>(vrow + ch * 8) = make_uint4(0u, 0u, 0u, 0u);  // finite: p = 0
+    }
+    cp_async_commit();
+  };
+  const int cq = (lane & 3) * 2;
+  int h_row[2];
+  bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (lane >> 2) + i * 8, hh = maps == 2 ? r & 7 : r;
+    valid[i] = hh < rep;
+    h_row[i] = g * rep + (valid[i] ? hh : 0);
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[NDVW][4];
+#pragma unroll
+  for (int i = 0; i < NDVW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+  const int lm = lane >> 3, lr = lane & 7;
+  const uint32_t a_lane = qs_addr + (uint32_t)((((lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (j_start + st * KT <= j_end) load_tile(st, j_start + st * KT);
+    else cp_async_commit();
+  }
+  int stage = 0;
+  for (int j0 = j_start; j0 <= j_end; j0 += KT, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+    {
+      const int jn = j0 + (STAGES - 1) * KT;
+      if (jn <= j_end) load_tile(stage == 0 ? STAGES - 1 : stage - 1, jn);
+      else cp_async_commit();
+      cp_async_wait<STAGES - 1>();
+    }
+    __syncthreads();  // the tile (and, first time round, Qs) is in shared memory
+    float s[2][4] = {}, s2[2][4] = {};
+    const uint32_t b_lane = ks_addr + (uint32_t)(((stage * KT + (lm >> 1) * 8 + lr) * KP + (lm & 1) * 8) * 2);
+    for (int kk = 0; kk < d; kk += 16) {
+      uint32_t a[4], bb[4];
+      ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
+      ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)(kk * 2));
+      mma_m16n8k16_bf16f32(s[0], a, bb[0], bb[1]);
+      mma_m16n8k16_bf16f32(s[1], a, bb[2], bb[3]);
+      if (maps == 2) {  // the second map's key columns; its rows are 8..15 of the tile
+        ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)((d + kk) * 2));
+        mma_m16n8k16_bf16f32(s2[0], a, bb[0], bb[1]);
+        mma_m16n8k16_bf16f32(s2[1], a, bb[2], bb[3]);
+      }
+    }
+    if (maps == 2) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        s[nt][2] = s2[nt][2];
+        s[nt][3] = s2[nt][3];
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
+        const int dist = p - j;
+        float v = s[nt][e];
+        if (dist < 0 || dist >= window || j > j_end) {
+          v = -INFINITY;
+        } else if (rel) {
+          v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+        }
+        s[nt][e] = v;
+        mx[i] = fmaxf(mx[i], v);
+      }
+    float m_use[2], corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m_run[i], mx[i]);
+      m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+      corr[i] = expf(m_run[i] - m_use[i]);
+      m_run[i] = m_new;
+    }
+    uint32_t pa[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(expf(s[nt][0] - m_use[0]), expf(s[nt][1] - m_use[0]));
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(expf(s[nt][2] - m_use[1]), expf(s[nt][3] - m_use[1]));
+      sum[0] += __low2float(lo) + __high2float(lo);   // the rounded probabilities: numerator and denominator see the same weights
+      sum[1] += __low2float(hi) + __high2float(hi);
+      pa[nt * 2] = *reinterpret_cast<const uint32_t*>(&lo);
+      pa[nt * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      l_run[i] = l_run[i] * corr[i] + sum[i];
+    }
+#pragma unroll
+    for (int i = 0; i < NDVW; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    const uint32_t v_lane = vs_addr + (uint32_t)(((stage * KT + (lm & 1) * 8 + lr) * VP + w * NDVW * 8 + (lm >> 1) * 8) * 2);
+#pragma unroll
+    for (int nt = 0; nt < NDVW; nt += 2) {
+      uint32_t bb[4];
+      ldmatrix_x4_trans(bb[0], bb[1], bb[2], bb[3], v_lane + (uint32_t)(nt * 8 * 2));
+      mma_m16n8k16_bf16f32(o[nt], pa, bb[0], bb[1]);
+      mma_m16n8k16_bf16f32(o[nt + 1], pa, bb[2], bb[3]);
+    }
+    __syncthreads();  // everyone is done with this stage before the next iteration's load overwrites it
+  }
+  // partial [token][g][split][16 rows][dv + 2]: unnormalised output, then the running max and sum (written by warp 0)
+  float* base = partial + ((((int64_t)t * gridDim.y + g) * gridDim.z + blockIdx.z) * kDecRows) * (dv + 2);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!valid[i]) continue;
+    float* dst = base + (int64_t)((lane >> 2) + i * 8) * (dv + 2);
+#pragma unroll
+    for (int nt = 0; nt < NDVW; ++nt) {
+      dst[(w * NDVW + nt) * 8 + cq] = o[nt][i * 2];
+      dst[(w * NDVW + nt) * 8 + cq + 1] = o[nt][i * 2 + 1];
+    }
+    if (w == 0 && (lane & 3) == 0) {
+      dst[dv] = m_run[i];
+      dst[dv + 1] = l_run[i];
+    }
+  }
+}
+
+// one block per (token, key/value head), one warp per row of the 16-row tile (rows beyond the group's are skipped)
+__global__ void __launch_bounds__(128) paged_heads_attn_dec_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, int H, int rep,
+                                                                        int maps, int dv, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const int g = blockIdx.y, lane = lane_id(), Hq = H * maps;
+  constexpr int kMaxSplit = 8;
+  for (int r = warp_id(); r < kDecRows; r += 4) {
+    const int mp = maps == 2 ? r >> 3 : 0, hh = maps == 2 ? r & 7 : r;
+    if (hh >= rep) continue;
+    const float* base = partial + ((((int64_t)t * gridDim.y + g) * nsplit) * kDecRows + r) * (dv + 2);
+    const int64_t zs = (int64_t)kDecRows * (dv + 2);
+    float M = -INFINITY, wz[kMaxSplit];
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = z < nsplit ? base[z * zs + dv] : -INFINITY;
+      M = fmaxf(M, wz[z]);
+    }
+    float den = 0.f;
+#pragma unroll
+    for (int z = 0; z < kMaxSplit; ++z) {
+      wz[z] = wz[z] > -INFINITY ? expf(wz[z] - M) : 0.f;  // an empty run carries no weight
+      if (z < nsplit) den += wz[z] * base[z * zs + dv + 1];
+    }
+    const float inv = 1.f / den;
+    float* dst = out + ((int64_t)t * Hq + (g * rep + hh) * maps + mp) * dv;
+    for (int c = lane; c < dv; c += 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int z = 0; z < kMaxSplit; ++z)
+        if (z < nsplit) acc = fmaf(wz[z], base[z * zs + c], acc);
+      dst[c] = acc * inv;
+    }
+  }
+}
+
 // in [T, H, 2, dv] fp32 (two maps per head) -> out [T, H * dv]: o = a1 - lambda a2, unit RMS over dv, times out_scale
 template <typename TO>
 __global__ void __launch_bounds__(256) diff_combine_kernel(const float* __restrict__ in, TO* __restrict__ out, int H, int dv, float lambda,
@@ -513,12 +748,30 @@ static bool attn_mma_shape_ok(int dt, int H, int G, int maps, int d, int dv) {
          dv % 16 == 0 && dv <= 256;
 }
 
-// Over how many blocks the tensor-core kernel should split every query tile's keys for this step (1: no split; 0: the shape takes
-// the plain kernel) and the fp32 workspace (`partial`) that takes: steps with few query rows (decoding) leave most SMs idle with one
+// steps of few rows whose head group fits one m16 tile take the decode form
+static bool attn_dec_ok(int dt, int64_t Tq, int H, int G, int maps, int d, int dv) {
+  if (!attn_mma_shape_ok(dt, H, G, maps, d, dv)) return false;
+  const int rep = H / G;
+  return dv % 64 == 0 && (maps == 2 ? rep <= 8 : rep <= 16) && Tq * G < 2 * 148;
+}
+
+// Over how many blocks the tensor-core kernels should split a query tile's keys for this step (1: no split; 0: the shape takes the
+// plain kernel) and the fp32 workspace (`partial`) that takes: steps with few query rows (decoding) would leave most SMs idle with one
 // block per (query tile, key/value head).
 extern "C" int b200_seq_paged_attn_splits(int dt, int64_t Tq, int B, int H, int G, int maps, int d, int dv, int64_t* workspace_floats) {
   if (workspace_floats) *workspace_floats = 0;
   if (!attn_mma_shape_ok(dt, H, G, maps, d, dv)) return 0;
+  if (attn_dec_ok(dt, Tq, H, G, maps, d, dv)) {
+    // as many runs as keep all blocks resident at once (shared memory decides how many share an SM): a second, thinner wave of
+    // blocks would double the time of a step that is bound by latency
+    const int64_t smem = ((int64_t)kDecRows * (d + kMmaPad) + (int64_t)kDecStages * kDecKT * ((maps * d + kMmaPad) + (dv + kMmaPad))) * 2 + 1024;
+    int64_t per_sm = (220 * 1024) / smem;
+    per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+    int64_t n = (148 * per_sm) / (Tq * G);
+    n = n < 2 ? 2 : (n > 8 ? 8 : n);
+    if (workspace_floats) *workspace_floats = Tq * G * n * kDecRows * (dv + 2);
+    return (int)n;
+  }
   const int QT = kMmaRows / ((H / G) * maps);
   const int64_t tiles = (Tq + QT - 1) / QT + B;
   const int64_t busy = ((Tq + QT - 1) / QT > B ? (Tq + QT - 1) / QT : B) * G;   // blocks that have rows: between the two bounds
@@ -547,29 +800,61 @@ extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, in
   if (window <= 0) window = 0x3fffffff;
   cudaStream_t st = (cudaStream_t)stream;
   const int rows_g = (H / G) * maps;
+  const bool aligned = row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0;
+  if (aligned && partial != nullptr && nsplit >= 2 && nsplit <= 8 && attn_dec_ok(dt, Tq, H, G, maps, d, dv)) {
+    const size_t smem = ((size_t)kDecRows * (d + kMmaPad) + (size_t)kDecStages * kDecKT * ((maps * d + kMmaPad) + (dv + kMmaPad))) * 2;
+    if (smem <= 200 * 1024) {
+      dim3 grid((unsigned)Tq, (unsigned)G, (unsigned)nsplit);
+#define PAD(N)                                                                                                                           \
+  do {                                                                                                                                   \
+    static bool cfg = false;                                                                                                             \
+    if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_dec_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
+    B200_LAUNCH((paged_heads_attn_dec_kernel<N>), grid, dim3(kMmaThreads), smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
+                block_table, bt_stride, seq_of_token, position_ids, out, H, H / G, maps, d, window, scale, page, rel, bucket_tab,         \
+                n_bucket_tab, rel_rows, partial);                                                                                        \
+    B200_LAUNCH(paged_heads_attn_dec_merge_kernel, dim3((unsigned)Tq, (unsigned)G), dim3(128), 0, st, (const float*)partial, out, H, H / G, \
+                maps, dv, nsplit);                                                                                                       \
+    b200_count_launches(2);                                                                                                              \
+    return B200_OK;                                                                                                                      \
+  } while (0)
+      switch (dv / 32) {
+        case 2: PAD(2);
+        case 4: PAD(4);
+        case 6: PAD(6);
+        case 8: PAD(8);
+        default: break;
+      }
+#undef PAD
+    }
+  }
   if (attn_mma_shape_ok(dt, H, G, maps, d, dv) && cu_q != nullptr && row_width % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
     const int QT = kMmaRows / rows_g;
     const int64_t tiles = (Tq + QT - 1) / QT + B;  // upper bound of sum_b ceil(n_b / QT); surplus blocks return at once
     const int kt = dv <= 128 ? 64 : 32;
-    const size_t smem = ((size_t)kMmaRows * (d + kMmaPad) + 2 * (size_t)kt * (maps * d + kMmaPad) + 2 * (size_t)kt * (dv + kMmaPad)) * 2;
+    const size_t stage_bytes = ((size_t)kt * (maps * d + kMmaPad) + (size_t)kt * (dv + kMmaPad)) * 2, q_bytes = (size_t)kMmaRows * (d + kMmaPad) * 2;
+    if (!partial || nsplit < 1) nsplit = 1;
+    if (nsplit > 8) nsplit = 8;
+    // two tile buffers: measured on B200 at 32 sequences x 1040 keys, five buffers (one block per SM instead of two) ran the
+    // split decode step 1.4x slower than two; the pipeline itself is written for any depth
+    constexpr int stages = 2;
+    const size_t smem = q_bytes + stages * stage_bytes;
     if (smem <= 200 * 1024 && tiles <= 0x7fffffff) {
-      if (!partial || nsplit < 1) nsplit = 1;
-      if (nsplit > 8) nsplit = 8;
       dim3 grid((unsigned)tiles, (unsigned)G, (unsigned)nsplit);
-#define PAM(N, KT)                                                                                                                       \
+#define PAM_S(N, KT, S)                                                                                                                  \
   do {                                                                                                                                   \
     static bool cfg = false;                                                                                                             \
-    if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_mma_kernel<N, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
-    B200_LAUNCH((paged_heads_attn_mma_kernel<N, KT>), grid, dim3(kMmaThreads), smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off, v_off, \
-                block_table, bt_stride, cu_q, position_ids, out, B, H, H / G, maps, d, window, scale, page, rel, bucket_tab, n_bucket_tab,  \
-                rel_rows, partial);                                                                                                      \
+    if (!cfg) { cudaFuncSetAttribute(paged_heads_attn_mma_kernel<N, KT, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); cfg = true; } \
+    B200_LAUNCH((paged_heads_attn_mma_kernel<N, KT, S>), grid, dim3(kMmaThreads), smem, st, q, (const __nv_bfloat16*)cache, row_width, k_off,  \
+                v_off, block_table, bt_stride, cu_q, position_ids, out, B, H, H / G, maps, d, window, scale, page, rel, bucket_tab,         \
+                n_bucket_tab, rel_rows, partial);                                                                                        \
     if (nsplit > 1)                                                                                                                      \
       B200_LAUNCH(paged_heads_attn_merge_kernel, dim3((unsigned)tiles, (unsigned)G), dim3(256), 0, st, (const float*)partial, out, cu_q, B, H, \
                   H / G, maps, dv, nsplit);                                                                                              \
     b200_count_launches(nsplit > 1 ? 2 : 1);                                                                                             \
     return B200_OK;                                                                                                                      \
   } while (0)
+#define PAM(N, KT) PAM_S(N, KT, stages)
       switch (dv / 8) {
         case 2: PAM(2, 64);
         case 4: PAM(4, 64);
@@ -589,6 +874,7 @@ extern "C" int b200_seq_paged_attn(const float* q, const void* cache, int dt, in
         case 32: PAM(32, 32);
         default: break;
       }
+#undef PAM_S
 #undef PAM
     }
   }
