@@ -81,11 +81,12 @@ int b200_seq_embed_add_pos(const void* table, const void* pos_table, int dt, con
 int b200_seq_rmsnorm_rows(const float* x, const void* w, int dt, float w_offset, void* out, int64_t T, int64_t W, float eps, void* stream);
 /* per token: unit-RMS (normalise != 0) of Hq query heads and Hk key heads of d elements, optional weights, queries times
  * 1 + temp_coef ln(floor((p + 1) / temp_every) + 1); keys to cache[slot, k_off ..], Cv values to cache[slot, v_off ..], queries to
- * q_out fp32 [T, Hq, d].  col_k / col_v < 0: the layer writes no keys / values */
+ * q_out fp32 [T, Hq, d].  col_k / col_v < 0: the layer writes no keys / values.  Inside a block of `page` tokens the pool is
+ * head-group-major: a group's k_group key heads (v_width value columns) of the block's tokens lie together */
 int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int d, const void* qnorm_w, float temp_coef, int temp_every,
                            int col_k, int Hk, const void* knorm_w, int col_v, int Cv, int normalise, const int64_t* position_ids,
-                           const int64_t* slot_mapping, void* cache, int dt, int64_t row_width, int k_off, int v_off, float* q_out, int64_t T,
-                           float eps, void* stream);
+                           const int64_t* slot_mapping, void* cache, int dt, int64_t row_width, int k_off, int v_off, int page, int k_group,
+                           int v_width, float* q_out, int64_t T, float eps, void* stream);
 /* soft-max attention of H * maps query rows per token over G * maps paged key heads (d) and G value heads (dv) of its own sequence,
  * causal, optional window, optional bias rel[bucket(distance), head] (fp32 [rel_rows, H]) after the scale; out fp32 [Tq, H * maps, dv] */
 int b200_seq_paged_attn(const float* q, const void* cache, int dt, int64_t row_width, int k_off, int v_off, const int32_t* block_table,

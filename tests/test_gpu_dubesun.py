@@ -159,7 +159,7 @@ def test_convolution_without_activation_any_cut(taps):
             assert torch.allclose(torch.cat(outs[b]).cpu().double(), refs[b], atol=1e-5), (taps, cuts, b)
 
 
-@pytest.mark.parametrize("E,top,ff", [(5, 2, 24), (3, 3, 70), (7, 1, 16), (40, 4, 8)])
+@pytest.mark.parametrize("E,top,ff", [(5, 2, 24), (3, 3, 70), (7, 1, 16), (40, 4, 8), (12, 10, 16)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_routed_experts_match_reference(E, top, ff, dtype):
     import tgis_b200  # noqa: F401
@@ -258,6 +258,21 @@ def test_mixer_alone_any_cut(kind, m, dtype):
             assert err < (2e-5 if dtype == torch.float32 else 0.08), (kind, cuts, b, err)
 
 
+def _fill_pool(cache, table, rows, kw, groups, kd, dv):
+    """token rows [L, kw + groups * dv] (keys of all heads, then values) -> the pool as the kernels read it: inside a block of
+    `page` tokens head-group-major - one group's keys of the block's tokens together, then the next group's, then the values"""
+    page = cache.shape[1]
+    host = cache.cpu().view(cache.shape[0], -1).clone()
+    for j in range(rows.shape[0]):
+        blk, tk = table[j // page], j % page
+        for g in range(groups):
+            o = g * page * kd + tk * kd
+            host[blk, o:o + kd] = rows[j, g * kd:(g + 1) * kd]
+            o = kw * page + g * page * dv + tk * dv
+            host[blk, o:o + dv] = rows[j, kw + g * dv:kw + (g + 1) * dv]
+    cache.copy_(host.view(cache.shape))
+
+
 def _attn_reference(q, krows, vrows, q_pos, H, G, maps, scale, rel=None, rows=0, far=0.0):
     """q [n, H * maps, d]; krows [L, G * maps, d]; vrows [L, G, dv]: dense soft-max per query over keys 0 .. its position"""
     rep = H // G
@@ -298,11 +313,8 @@ def test_paged_attention_far_keys_page_borders_first_tokens(dtype, maps, H, G, d
     ref = _attn_reference(q, krows, vrows, q_pos, H, G, maps, scale)
     perm = torch.randperm(32, generator=g).tolist()   # the sequence's pages lie out of order in the pool
     table = perm[:(L + 15) // 16]
-    cache = torch.full((32, 16, KW + VW), float("nan"), dtype=dtype, device=DEV)
-    for blk in range(len(table)):
-        n = min(16, L - blk * 16)
-        cache[table[blk], :n] = rows[blk * 16:blk * 16 + n].to(DEV)
-    cache = torch.nan_to_num(cache, nan=1e4)  # rows that belong to nobody are loud but finite
+    cache = torch.full((32, 16, KW + VW), 1e4, dtype=dtype, device=DEV)  # rows that belong to nobody are loud but finite
+    _fill_pool(cache, table, rows, KW, G, maps * d, dv)
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     for i, p in enumerate(q_pos):
         st = _step([(p, 1)], [table])
@@ -334,8 +346,8 @@ def test_distance_bias_bucket_edges(rows, far, dtype, d):
     tab_t = torch.tensor(tab, dtype=torch.int32, device=DEV)
     kv = (torch.randn(L, 2 * d, generator=g) * 0.3).to(dtype).float()
     cache = torch.zeros(20, 16, 2 * d, dtype=dtype, device=DEV)
-    cache.view(-1, 2 * d)[:L] = kv.to(DEV)
     table = list(range(19))
+    _fill_pool(cache, table, kv.to(dtype), d, 1, d, d)
     krows, vrows = kv[:, :d].view(L, 1, d), kv[:, d:].view(L, 1, d)
     for loud in sorted({0, rows // 2 - 1, rows // 2, rows - 2, rows - 1}):
         rel = torch.randn(rows, H, generator=g) * 0.2

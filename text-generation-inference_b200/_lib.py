@@ -145,7 +145,7 @@ SEQ_SIGNATURES = {
     "b200_seq_causal_conv": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _P]),
     "b200_seq_embed_add_pos": (_I, [_P, _P, _I, _P, _P, _P, _L, _L, _L, _L, _P]),
     "b200_seq_rmsnorm_rows": (_I, [_P, _P, _I, _F, _P, _L, _L, _F, _P]),
-    "b200_seq_heads_prepare": (_I, [_P, _L, _I, _I, _I, _P, _F, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _I, _L, _I, _I, _P, _L, _F, _P]),
+    "b200_seq_heads_prepare": (_I, [_P, _L, _I, _I, _I, _P, _F, _I, _I, _I, _P, _I, _I, _I, _P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _L, _F, _P]),
     "b200_seq_paged_attn": (_I, [_P, _P, _I, _L, _I, _I, _P, _L, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _I, _I, _P, _I, _P]),
     "b200_seq_paged_attn_splits": (_I, [_I, _L, _I, _I, _I, _I, _I, _I, ctypes.POINTER(c_int64)]),
     "b200_seq_diff_combine": (_I, [_P, _P, _I, _L, _I, _I, _F, _F, _F, _P]),

@@ -20,7 +20,7 @@
 namespace b200 {
 namespace seq {
 
-constexpr int kMoeTile = 64, kMoeStep = 16, kMaxTop = 8, kMaxExpertsPerLane = 8;
+constexpr int kMoeTile = 64, kMoeStep = 16, kMaxTop = 16, kMaxExpertsPerLane = 8;
 
 struct MoePlan {
   int32_t *counts, *offsets, *n_tiles, *tile_expert, *tile_row0, *place, *row_of, *token_of_row;
@@ -307,7 +307,7 @@ extern "C" int64_t b200_seq_moe_plan_ints(int64_t T, int E, int top) {
 extern "C" int b200_seq_moe_route(const float* logits, int64_t T, int E, int top, int32_t* ids, float* weights, int32_t* plan, void* stream) {
   if (T == 0) return B200_OK;
   if (E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 || top > kMaxTop || top > E) {
-    b200_set_last_error("seq_moe_route: need 1 <= top <= min(8, experts), experts <= 256");
+    b200_set_last_error("seq_moe_route: need 1 <= top <= min(16, experts), experts <= 256");
     return B200_ERR_ARG;
   }
   cudaStream_t st = (cudaStream_t)stream;

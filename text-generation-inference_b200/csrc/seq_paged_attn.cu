@@ -1,5 +1,8 @@
-// Multi-head attention over paged per-head keys and values, for decoders whose layers cache one row per token:
-//   cache row = [ ... keys of every key head (k_off) ... | ... values of every value head (v_off) ... ]   (any widths, one element type)
+// Multi-head attention over paged per-head keys and values, for decoders whose layers cache `row_width` elements per token:
+//   columns of a token = [ ... keys of every key head (from k_off) ... | ... values of every value head (from v_off) ... ]
+// Inside a block of `page` tokens the pool is head-group-major: the keys that one key/value head group needs of the block's tokens
+// lie together (page x (maps * dim) elements), then the next group's, and after all keys the values likewise (page x vdim each), so
+// a block reading one group's keys or values of consecutive tokens reads consecutive memory (head_slice_base below).
 //
 //   heads_prepare_kernel : from a token's projected (and, where the layer has one, convolved) row: RMS-norms every query head and
 //                          key head over its `d` elements (optional weight), multiplies the queries by the position's temperature
@@ -23,11 +26,17 @@ namespace seq {
 
 constexpr int kPrepThreads = 256;
 
+// first element of token `tk` of block `block` in slice `slice` (w columns wide) of the column region that starts at column `off`
+__device__ __forceinline__ int64_t head_slice_base(int64_t block, int tk, int page, int64_t RW, int off, int slice, int w) {
+  return block * page * RW + (int64_t)off * page + (int64_t)slice * page * w + (int64_t)tk * w;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kPrepThreads) heads_prepare_kernel(
     const float* __restrict__ src, int64_t ld, int col_q, int Hq, int d, const T* __restrict__ qnorm_w, float temp_coef, int temp_every,
     int col_k, int Hk, const T* __restrict__ knorm_w, int col_v, int Cv, int normalise, const int64_t* __restrict__ position_ids,
-    const int64_t* __restrict__ slot_mapping, T* __restrict__ cache, int64_t RW, int k_off, int v_off, float* __restrict__ q_out, float eps) {
+    const int64_t* __restrict__ slot_mapping, T* __restrict__ cache, int64_t RW, int k_off, int v_off, int page, int k_group, int v_w,
+    float* __restrict__ q_out, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t t = blockIdx.x;
@@ -53,13 +62,13 @@ __global__ void __launch_bounds__(kPrepThreads) heads_prepare_kernel(
       float* dst = q_out + (t * Hq + h) * d;
       for (int i = lane; i < d; i += 32) dst[i] = v[i] * rstd * (nw_ptr ? ldf(nw_ptr + i) : 1.f) * temp;
     } else if (slot >= 0) {
-      T* dst = cache + slot * RW + k_off + (int64_t)h * d;
+      T* dst = cache + head_slice_base(slot / page, (int)(slot % page), page, RW, k_off, h / k_group, k_group * d) + (h % k_group) * d;
       for (int i = lane; i < d; i += 32) stf(dst + i, v[i] * rstd * (nw_ptr ? ldf(nw_ptr + i) : 1.f));
     }
   }
   if (col_v >= 0 && slot >= 0) {
-    T* dst = cache + slot * RW + v_off;
-    for (int i = threadIdx.x; i < Cv; i += kPrepThreads) stf(dst + i, row[col_v + i]);
+    for (int i = threadIdx.x; i < Cv; i += kPrepThreads)
+      stf(cache + head_slice_base(slot / page, (int)(slot % page), page, RW, v_off, i / v_w, v_w) + i % v_w, row[col_v + i]);
   }
 }
 
@@ -112,14 +121,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_heads_attn_kernel(
     for (int idx = threadIdx.x; idx < nk * KD; idx += nthreads) {
       const int jj = idx / KD, dd = idx % KD;
       const int j = j0 + jj;
-      const int64_t row = (int64_t)table[j / page] * page + j % page;
-      ks[jj * KP + dd] = ldf(cache + row * RW + k_off + (int64_t)g * KD + dd);
+      ks[jj * KP + dd] = ldf(cache + head_slice_base(table[j / page], j % page, page, RW, k_off, g, KD) + dd);
     }
     for (int idx = threadIdx.x; idx < nk * dv; idx += nthreads) {
       const int jj = idx / dv, dd = idx % dv;
       const int j = j0 + jj;
-      const int64_t row = (int64_t)table[j / page] * page + j % page;
-      vs[jj * dv + dd] = ldf(cache + row * RW + v_off + (int64_t)g * dv + dd);
+      vs[jj * dv + dd] = ldf(cache + head_slice_base(table[j / page], j % page, page, RW, v_off, g, dv) + dd);
     }
     __syncthreads();
 #pragma unroll
@@ -243,10 +250,10 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
       __nv_bfloat16* krow = kd + row * KP;
       __nv_bfloat16* vrow = vd + row * VP;
       if (j <= j_end) {
-        const int64_t crow = page_shift >= 0 ? ((int64_t)table[j >> page_shift] << page_shift) + (j & (page - 1))
-                                             : (int64_t)table[j / page] * page + j % page;
-        const __nv_bfloat16* ksrc = cache + crow * RW + k_off + (int64_t)g * KD;
-        const __nv_bfloat16* vsrc = cache + crow * RW + v_off + (int64_t)g * dv;
+        const int64_t blk = table[page_shift >= 0 ? j >> page_shift : j / page];
+        const int tk = page_shift >= 0 ? j & (page - 1) : j % page;
+        const __nv_bfloat16* ksrc = cache + head_slice_base(blk, tk, page, RW, k_off, g, KD);
+        const __nv_bfloat16* vsrc = cache + head_slice_base(blk, tk, page, RW, v_off, g, dv);
         for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, ksrc + ch * 8, true);
         for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, vsrc + ch * 8, true);
       } else {
@@ -267,6 +274,7 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
     p_row[i] = valid[i] ? p0 + tok : p0;
     h_row[i] = g * rep + rr % rep;
   }
+  const float rel_far[2] = {rel ? rel[(rel_rows - 1) * H + h_row[0]] : 0.f, rel ? rel[(rel_rows - 1) * H + h_row[1]] : 0.f};
   const int mp_w = (w * 16) / rpm;
   const bool warp_active = ((w * 16) % rpm) / rep < ntok;  // rows of a warp ascend in token: its first row decides
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -309,21 +317,32 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_mma_kernel(
         }
       }
       float mx[2] = {-INFINITY, -INFINITY};
+      if (j0 + KT - 1 <= min(j_end, p0) && p_last - j0 < window && (!rel || p0 - (j0 + KT - 1) >= n_bucket_tab)) {
+        // an interior tile: every key is visible to every row and (with a bias) lies in the last bucket
 #pragma unroll
-      for (int nt = 0; nt < KT / 8; ++nt)
+        for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
-          const int dist = p_row[i] - j;
-          float v = s[nt][e];
-          if (dist < 0 || dist >= window || j > j_end) {
-            v = -INFINITY;
-          } else if (rel) {
-            v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+          for (int e = 0; e < 4; ++e) {
+            s[nt][e] += rel_far[e >> 1];
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
           }
-          s[nt][e] = v;
-          mx[i] = fmaxf(mx[i], v);
-        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
+            const int dist = p_row[i] - j;
+            float v = s[nt][e];
+            if (dist < 0 || dist >= window || j > j_end) {
+              v = -INFINITY;
+            } else if (rel) {
+              v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+            }
+            s[nt][e] = v;
+            mx[i] = fmaxf(mx[i], v);
+          }
+      }
       float m_use[2], corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -460,7 +479,7 @@ __global__ void __launch_bounds__(256) paged_heads_attn_merge_kernel(const float
 // run of the token's keys): the token's rows of that head group - (rep query heads) x maps, at most 16 - are ONE m16 tile; rows
 // 0..7 carry map 1 and rows 8..15 map 2 when there are two maps.  Every warp scores the whole 16-key tile (the same S in all four:
 // a few MMAs) and keeps the same running max and sum, but accumulates only its quarter of the value columns, so a thread holds
-// vdim / 16 output values instead of vdim / 2 and several blocks share an SM, each with STAGES - 1 small tiles in flight: the
+// vdim / 16 output values instead of vdim / 2 and several blocks share an SM, each with three small tiles in flight: the
 // key / value stream of a decoding step is bound by memory latency, not by work.  Partials per run are merged by
 // paged_heads_attn_dec_merge_kernel.  Needs dim % 16 == 0, vdim % 64 == 0, rep * maps <= 16 (rep <= 8 with two maps).
 // ------------------------------------------------------------------------------------------------------------------------
@@ -506,10 +525,10 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
     __nv_bfloat16* krow = Ks + (stage * KT + row) * KP;
     __nv_bfloat16* vrow = Vs + (stage * KT + row) * VP;
     if (j <= j_end) {
-      const int64_t crow = page_shift >= 0 ? ((int64_t)table[j >> page_shift] << page_shift) + (j & (page - 1))
-                                           : (int64_t)table[j / page] * page + j % page;
-      const __nv_bfloat16* ksrc = cache + crow * RW + k_off + (int64_t)g * KD;
-      const __nv_bfloat16* vsrc = cache + crow * RW + v_off + (int64_t)g * dv;
+      const int64_t blk = table[page_shift >= 0 ? j >> page_shift : j / page];
+      const int tk = page_shift >= 0 ? j & (page - 1) : j % page;
+      const __nv_bfloat16* ksrc = cache + head_slice_base(blk, tk, page, RW, k_off, g, KD);
+      const __nv_bfloat16* vsrc = cache + head_slice_base(blk, tk, page, RW, v_off, g, dv);
       for (int ch = threadIdx.x & 7; ch < kchunks; ch += 8) cp_async_16(krow + ch * 8, ksrc + ch * 8, true);
       for (int ch = threadIdx.x & 7; ch < vchunks; ch += 8) cp_async_16(vrow + ch * 8, vsrc + ch * 8, true);
     } else {
@@ -527,6 +546,7 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
     valid[i] = hh < rep;
     h_row[i] = g * rep + (valid[i] ? hh : 0);
   }
+  const float rel_far[2] = {rel ? rel[(rel_rows - 1) * H + h_row[0]] : 0.f, rel ? rel[(rel_rows - 1) * H + h_row[1]] : 0.f};
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[NDVW][4];
 #pragma unroll
@@ -534,6 +554,8 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
   const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
   const int lm = lane >> 3, lr = lane & 7;
   const uint32_t a_lane = qs_addr + (uint32_t)((((lm & 1) * 8 + lr) * DP + (lm >> 1) * 8) * 2);
+  // STAGES - 1 tiles are in flight ahead of the one being used; every iteration commits one group (an empty one past the end),
+  // so "at most STAGES - 1 groups pending" always means that the current tile has landed
 #pragma unroll
   for (int st = 0; st < STAGES - 1; ++st) {
     if (j_start + st * KT <= j_end) load_tile(st, j_start + st * KT);
@@ -548,43 +570,70 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
       cp_async_wait<STAGES - 1>();
     }
     __syncthreads();  // the tile (and, first time round, Qs) is in shared memory
-    float s[2][4] = {}, s2[2][4] = {};
+    // the score products: even and odd k steps accumulate apart (two short chains of dependent MMAs instead of one long one)
+    float s[2][4] = {}, s2[2][4] = {}, t1[2][4] = {}, t2[2][4] = {};
     const uint32_t b_lane = ks_addr + (uint32_t)(((stage * KT + (lm >> 1) * 8 + lr) * KP + (lm & 1) * 8) * 2);
-    for (int kk = 0; kk < d; kk += 16) {
-      uint32_t a[4], bb[4];
+#pragma unroll 2
+    for (int kk = 0; kk < d; kk += 32) {
+      uint32_t a[4], bb[4], a2[4], b2[4];
+      const bool odd = kk + 16 < d;
       ldmatrix_x4(a[0], a[1], a[2], a[3], a_lane + kk * 2);
       ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)(kk * 2));
+      if (odd) {
+        ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], a_lane + (kk + 16) * 2);
+        ldmatrix_x4(b2[0], b2[1], b2[2], b2[3], b_lane + (uint32_t)((kk + 16) * 2));
+      }
       mma_m16n8k16_bf16f32(s[0], a, bb[0], bb[1]);
       mma_m16n8k16_bf16f32(s[1], a, bb[2], bb[3]);
+      if (odd) {
+        mma_m16n8k16_bf16f32(t1[0], a2, b2[0], b2[1]);
+        mma_m16n8k16_bf16f32(t1[1], a2, b2[2], b2[3]);
+      }
       if (maps == 2) {  // the second map's key columns; its rows are 8..15 of the tile
         ldmatrix_x4(bb[0], bb[1], bb[2], bb[3], b_lane + (uint32_t)((d + kk) * 2));
+        if (odd) ldmatrix_x4(b2[0], b2[1], b2[2], b2[3], b_lane + (uint32_t)((d + kk + 16) * 2));
         mma_m16n8k16_bf16f32(s2[0], a, bb[0], bb[1]);
         mma_m16n8k16_bf16f32(s2[1], a, bb[2], bb[3]);
+        if (odd) {
+          mma_m16n8k16_bf16f32(t2[0], a2, b2[0], b2[1]);
+          mma_m16n8k16_bf16f32(t2[1], a2, b2[2], b2[3]);
+        }
       }
     }
-    if (maps == 2) {
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        s[nt][2] = s2[nt][2];
-        s[nt][3] = s2[nt][3];
-      }
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][0] += t1[nt][0];
+      s[nt][1] += t1[nt][1];
+      s[nt][2] = maps == 2 ? s2[nt][2] + t2[nt][2] : s[nt][2] + t1[nt][2];
+      s[nt][3] = maps == 2 ? s2[nt][3] + t2[nt][3] : s[nt][3] + t1[nt][3];
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    if (j0 + KT - 1 <= j_end && p - j0 < window && (!rel || p - (j0 + KT - 1) >= n_bucket_tab)) {
+      // an interior tile: every key is visible and (with a bias) lies in the last bucket - no per-element mask or lookup
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
-        const int dist = p - j;
-        float v = s[nt][e];
-        if (dist < 0 || dist >= window || j > j_end) {
-          v = -INFINITY;
-        } else if (rel) {
-          v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+        for (int e = 0; e < 4; ++e) {
+          s[nt][e] += rel_far[e >> 1];
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
         }
-        s[nt][e] = v;
-        mx[i] = fmaxf(mx[i], v);
-      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1, j = j0 + nt * 8 + cq + (e & 1);
+          const int dist = p - j;
+          float v = s[nt][e];
+          if (dist < 0 || dist >= window || j > j_end) {
+            v = -INFINITY;
+          } else if (rel) {
+            v += rel[(dist < n_bucket_tab ? bucket_tab[dist] : rel_rows - 1) * H + h_row[i]];
+          }
+          s[nt][e] = v;
+          mx[i] = fmaxf(mx[i], v);
+        }
+    }
     float m_use[2], corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -611,12 +660,14 @@ __global__ void __launch_bounds__(kMmaThreads) paged_heads_attn_dec_kernel(
       sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
       l_run[i] = l_run[i] * corr[i] + sum[i];
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // the running maxima settle after the first tiles
 #pragma unroll
-    for (int i = 0; i < NDVW; ++i) {
-      o[i][0] *= corr[0];
-      o[i][1] *= corr[0];
-      o[i][2] *= corr[1];
-      o[i][3] *= corr[1];
+      for (int i = 0; i < NDVW; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
     }
     const uint32_t v_lane = vs_addr + (uint32_t)(((stage * KT + (lm & 1) * 8 + lr) * VP + w * NDVW * 8 + (lm >> 1) * 8) * 2);
 #pragma unroll
@@ -712,15 +763,21 @@ using namespace b200::seq;
 // src: fp32 rows (leading dimension ld) holding Hq query heads of d elements from col_q, Hk key heads from col_k (col_k < 0: the
 // layer writes no keys), Cv value elements from col_v (col_v < 0: no values).  normalise != 0: unit RMS over d per head (eps), times
 // the weight when given.  Queries are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) (temp_coef 0: by 1).
+// The pool is written head-group-major inside a block of `page` tokens: k_group key heads and v_width value columns per group.
 extern "C" int b200_seq_heads_prepare(const float* src, int64_t ld, int col_q, int Hq, int d, const void* qnorm_w, float temp_coef,
                                       int temp_every, int col_k, int Hk, const void* knorm_w, int col_v, int Cv, int normalise,
                                       const int64_t* position_ids, const int64_t* slot_mapping, void* cache, int dt, int64_t row_width,
-                                      int k_off, int v_off, float* q_out, int64_t T, float eps, void* stream) {
+                                      int k_off, int v_off, int page, int k_group, int v_width, float* q_out, int64_t T, float eps,
+                                      void* stream) {
   if (T == 0) return B200_OK;
-  if (Hq <= 0 || d <= 0) { b200_set_last_error("seq_heads_prepare: bad sizes"); return B200_ERR_ARG; }
+  if (Hq <= 0 || d <= 0 || page <= 0 || (col_k >= 0 && (k_group <= 0 || Hk % k_group != 0)) || (col_v >= 0 && (v_width <= 0 || Cv % v_width != 0))) {
+    b200_set_last_error("seq_heads_prepare: bad sizes");
+    return B200_ERR_ARG;
+  }
   B200_SEQ_DISPATCH(dt, E, B200_LAUNCH((heads_prepare_kernel<E>), dim3((unsigned)T), dim3(kPrepThreads), 0, (cudaStream_t)stream, src, ld, col_q, Hq,
                                        d, (const E*)qnorm_w, temp_coef, temp_every, col_k, Hk, (const E*)knorm_w, col_v, Cv, normalise,
-                                       position_ids, slot_mapping, (E*)cache, row_width, k_off, v_off, q_out, eps));
+                                       position_ids, slot_mapping, (E*)cache, row_width, k_off, v_off, page, k_group > 0 ? k_group : 1,
+                                       v_width > 0 ? v_width : 1, q_out, eps));
   b200_count_launches(1);
   return B200_OK;
 }

@@ -292,25 +292,27 @@ def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, w_offset: float =
 
 def heads_prepare(src: torch.Tensor, *, col_q: int, q_heads: int, dim: int, q_norm_w: Optional[torch.Tensor], temp_coef: float, temp_every: int,
                   col_k: int, k_heads: int, k_norm_w: Optional[torch.Tensor], col_v: int, v_width: int, normalise: bool, step: RaggedStep,
-                  cache: torch.Tensor, k_off: int, v_off: int, eps: float) -> torch.Tensor:
+                  cache: torch.Tensor, k_off: int, v_off: int, k_group: int, v_group_width: int, eps: float) -> torch.Tensor:
     """src fp32 [T, C]: unit-RMS per head (optional weight) of the query heads at col_q and the key heads at col_k, the queries times
     the position's temperature; keys -> cache[slot, k_off:], v_width values from col_v -> cache[slot, v_off:]; -> queries fp32
-    [T, q_heads, dim].  col_k / col_v < 0: the layer writes no keys / values (it reads another layer's rows)."""
+    [T, q_heads, dim].  col_k / col_v < 0: the layer writes no keys / values (it reads another layer's rows).  Inside a block the
+    pool is head-group-major (what `paged_attn` reads): `k_group` key heads and `v_group_width` value columns per key/value head
+    group; of a block's tokens, one group's keys lie together, then the next group's, and after all keys the values likewise."""
     _cuda(src, cache, q_norm_w, k_norm_w)
     assert src.dtype == torch.float32 and src.stride(1) == 1 and cache.is_contiguous()
     q = torch.empty(step.T, q_heads, dim, dtype=torch.float32, device=src.device)
     _lib.check_seq(_lib.load_seq().b200_seq_heads_prepare(
         _ptr(src), src.stride(0), col_q, q_heads, dim, _ptr(q_norm_w), float(temp_coef), int(temp_every), col_k, k_heads, _ptr(k_norm_w), col_v,
         v_width, int(normalise), _ptr(step.position_ids), _ptr(step.slot_mapping), _ptr(cache), _dt(cache), cache.shape[-1], k_off, v_off,
-        _ptr(q), step.T, float(eps), _stream()), "seq_heads_prepare")
+        cache.shape[1], int(k_group), int(v_group_width), _ptr(q), step.T, float(eps), _stream()), "seq_heads_prepare")
     return q
 
 
 def paged_attn(q: torch.Tensor, cache: torch.Tensor, step: RaggedStep, *, heads: int, kv_heads: int, maps: int, vdim: int, k_off: int,
                v_off: int, scale: float, window: int = 0, rel: Optional[torch.Tensor] = None, bucket_tab: Optional[torch.Tensor] = None
                ) -> torch.Tensor:
-    """q fp32 [T, heads * maps, dim]; cache [blocks, page, row] with kv_heads * maps key heads at k_off and kv_heads value heads (vdim)
-    at v_off -> fp32 [T, heads * maps, vdim]: causal soft-max attention of every token over its own sequence's cache rows.
+    """q fp32 [T, heads * maps, dim]; cache [blocks, page, row] (head-group-major inside a block, as `heads_prepare` writes it) with
+    kv_heads * maps key heads from column k_off and kv_heads value heads (vdim) from column v_off -> fp32 [T, heads * maps, vdim]: causal soft-max attention of every token over its own sequence's cache rows.
     rel fp32 [rows, heads] + bucket_tab int32 [n]: rel[bucket(i - j), head] is added to the scaled score, bucket(n) = bucket_tab[n]
     below len(bucket_tab), rows - 1 from there on."""
     _cuda(q, cache, rel, bucket_tab)

@@ -204,7 +204,8 @@ class DifferentialAttention(nn.Module):
     (1 - diff); lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff.  Queries and keys hold [map 1 | map 2] per head.  A depth-wise
     causal convolution (`conv` taps, no bias) follows each of the q / k / v projections; queries and keys are then RMS-normed per
     head and map with a weight shared by all heads, and queries are multiplied by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1).
-    No rotation.  Per sequence: a cache row [keys after convolution and norm | values after convolution] per token and the last
+    No rotation.  Per sequence and token: the keys after convolution and norm and the values after convolution in the block pool
+    (head-group-major inside a block, ops_seq.heads_prepare), and the last
     conv - 1 projected rows (fp32 state slot).  `own_kv` False: the layer has no key / value tensors and reads the rows of another
     layer with the same head counts (its `forward` is given that layer's pool).
     Tensors under `prefix`: q, q.conv, q.norm, [k, k.conv, k.norm, v, v.conv,] lq1, lk1, lq2, lk2, o."""
@@ -245,7 +246,7 @@ class DifferentialAttention(nn.Module):
         q = ops.heads_prepare(c, col_q=0, q_heads=self.H * 2, dim=self.d, q_norm_w=self.q_norm, temp_coef=self.temp_coef,
                               temp_every=self.temp_every, col_k=self.cq if own else -1, k_heads=self.G * 2, k_norm_w=self.k_norm,
                               col_v=self.cq + self.ck if own else -1, v_width=self.cv, normalise=True, step=step, cache=pages, k_off=0,
-                              v_off=self.ck, eps=self.eps)
+                              v_off=self.ck, k_group=2, v_group_width=self.dv, eps=self.eps)
         a = ops.paged_attn(q, pages, step, heads=self.H, kv_heads=self.G, maps=2, vdim=self.dv, k_off=0, v_off=self.ck, scale=self.scale,
                            window=self.window)
         o = ops.diff_combine(a, self.H, self.dv, self.lam, 1.0 - self.diff, self.eps, self.dtype)
@@ -256,7 +257,7 @@ class BucketBiasAttention(nn.Module):
     """Grouped-query attention whose values are the keys as projected (there is no value projection), with biases on the q / k
     projections, queries and keys divided by their RMS per head (no weight), a learned bias rel[bucket(i - j), head] added to the
     scaled score (`log_distance_buckets` over the table's rows and `bias_max`), and sigmoid(W_g h) multiplied into the concatenated
-    heads before the output projection.  No rotation.  Cache row per token: [unit-RMS keys | keys as projected].
+    heads before the output projection.  No rotation.  Cached per token: the unit-RMS keys and the keys as projected (the values).
     Tensors under `prefix`: q, q.b, k, k.b, rel, g, o."""
 
     def __init__(self, prefix: str, weights, *, heads: int, kv_heads: int, dim: int, scale: float, bias_max: float, eps: float,
@@ -284,7 +285,8 @@ class BucketBiasAttention(nn.Module):
         H, G, d = self.H, self.G, self.d
         u = ops.linear(h, self.w_in, self.b_in, out_dtype=torch.float32)
         q = ops.heads_prepare(u, col_q=0, q_heads=H, dim=d, q_norm_w=None, temp_coef=0.0, temp_every=0, col_k=H * d, k_heads=G, k_norm_w=None,
-                              col_v=H * d, v_width=G * d, normalise=True, step=step, cache=pages, k_off=0, v_off=G * d, eps=self.eps)
+                              col_v=H * d, v_width=G * d, normalise=True, step=step, cache=pages, k_off=0, v_off=G * d, k_group=1,
+                              v_group_width=d, eps=self.eps)
         a = ops.paged_attn(q, pages, step, heads=H, kv_heads=G, maps=1, vdim=d, k_off=0, v_off=G * d, scale=self.scale, window=self.window,
                            rel=self.rel, bucket_tab=self.bucket_tab)
         gated = ops.group_rmsnorm_gate(a.view(step.T, H * d), None, 0, self.eps, self.dtype, gate=u[:, (H + G) * d:],

@@ -300,7 +300,8 @@ class HybridCacheManager(PagedKVCacheManager):
 
     Same block bookkeeping as the KV manager (allocator, per-sequence block lists, reference counts, block tables, slot mapping),
     but every layer says what it stores: a paged layer gets its own pool [num_blocks, block_size, row_width] of the model's element
-    type (one row per token, no head dimension: e.g. the latent + rotated key part of latent attention), a state layer gets fp32
+    type (`row_width` elements per token; how a block's elements are ordered is up to the kernels of the mixer: token-major rows for
+    the latent + rotated key part of latent attention, head-group-major for per-head keys and values), a state layer gets fp32
     tensors [num_state_slots, *shape].  A sequence takes one state slot when it is created and gives it back, with its blocks,
     in `free_sequences`; slots are not cleared on reuse: the kernels start a sequence at position 0 from a zero state without
     reading the slot."""
